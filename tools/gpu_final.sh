@@ -8,5 +8,5 @@ echo "== bench reference arm"; timeout 600 python bench.py --impl reference --st
 TAG=r01d
 KREG='k_w4a16|k_add_rmsnorm|k_decode_attn|k_qkv_rope|k_dense|k_argmax|k_embedding|k_attn_combine|k_rope_cos|k_lens|k_advance|k_gate'
 timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none -k regex:"$KREG" -s 1500 -c 600 --csv --log-file gpurun_out/${TAG}_launches.csv python bench.py --steps 2 --warmup 3 --prompt 2 --no-cpu-baseline --requests 0 > gpurun_out/${TAG}_ncu_bench.log 2>&1; echo "launch list rc=$?"
-timeout 600 ncu --set full --clock-control none --import-source on -k regex:k_w4a16 -s 300 -c 4 -f -o gpurun_out/${TAG}_prof_w4a16 python bench.py --steps 2 --warmup 3 --prompt 2 --no-cpu-baseline --requests 0 > gpurun_out/${TAG}_ncu_full.log 2>&1; echo "full rc=$?"
+timeout 600 ncu --set full --clock-control none -k regex:k_w4a16 -s 300 -c 4 -f -o gpurun_out/${TAG}_prof_w4a16 python bench.py --steps 2 --warmup 3 --prompt 2 --no-cpu-baseline --requests 0 > gpurun_out/${TAG}_ncu_full.log 2>&1; echo "full rc=$?"
 ZL_W4_DEBUG=10 LAYERS=8 timeout 200 python tools/trace_step.py > gpurun_out/r01_inchain_timeline.txt 2>&1; tail -6 gpurun_out/r01_inchain_timeline.txt

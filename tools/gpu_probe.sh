@@ -11,5 +11,5 @@ echo "== stream probe (no dequant/MMA)"; ZL_W4_DEBUG=1 run probe ""
 ZL_W4_DEBUG=1 ZL_DEBUG_SKIP=1 run probe_noattn ""
 echo "== ncu v2"
 TAG=r01b
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:k_w4a16_v2 -s 300 -c 4 -f -o gpurun_out/${TAG}_prof_w4a16 python bench.py --steps 2 --warmup 3 --prompt 2 --no-cpu-baseline > gpurun_out/${TAG}_ncu_full.log 2>&1; echo "full rc=$?"
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:k_decode_attn -s 40 -c 2 -f -o gpurun_out/${TAG}_prof_attn python bench.py --steps 2 --warmup 3 --prompt 200 --no-cpu-baseline > gpurun_out/${TAG}_ncu_attn.log 2>&1; echo "attn rc=$?"
+timeout 900 ncu --set full --clock-control none -k regex:k_w4a16_v2 -s 300 -c 4 -f -o gpurun_out/${TAG}_prof_w4a16 python bench.py --steps 2 --warmup 3 --prompt 2 --no-cpu-baseline > gpurun_out/${TAG}_ncu_full.log 2>&1; echo "full rc=$?"
+timeout 900 ncu --set full --clock-control none -k regex:k_decode_attn -s 40 -c 2 -f -o gpurun_out/${TAG}_prof_attn python bench.py --steps 2 --warmup 3 --prompt 200 --no-cpu-baseline > gpurun_out/${TAG}_ncu_attn.log 2>&1; echo "attn rc=$?"

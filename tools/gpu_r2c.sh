@@ -16,6 +16,6 @@ for l in open('gpurun_out/r2c/tc_bench_graph.jsonl'):
 PY
 tail -3 $O/tc_bench_graph.err
 echo "== ncu tc kernel"
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:k_w4a16_tc -s 6 -c 2 -o $O/tc_prof python tools/tc_bench.py --one 28672 4096 32 > $O/ncu_tc.log 2>&1; tail -3 $O/ncu_tc.log
+timeout 900 ncu --set full --clock-control none -k regex:k_w4a16_tc -s 6 -c 2 -o $O/tc_prof python tools/tc_bench.py --one 28672 4096 32 > $O/ncu_tc.log 2>&1; tail -3 $O/ncu_tc.log
 echo "== attention bench"; timeout 600 python tools/attn_bench.py > $O/attn_bench.jsonl 2>$O/attn_bench.err; cat $O/attn_bench.jsonl; tail -3 $O/attn_bench.err
 echo "== w8 bench"; timeout 600 python tools/w8_bench.py > $O/w8_bench.txt 2>&1; tail -24 $O/w8_bench.txt

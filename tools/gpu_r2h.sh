@@ -24,4 +24,4 @@ for l in sys.stdin:
 echo "== timeline mask 70"; ZL_NO_PDL_MASK=70 timeout 300 python tools/trace_step.py > $O/timeline70.txt 2>&1; tail -4 $O/timeline70.txt
 echo "== timeline mask 66 (o with PDL)"; ZL_NO_PDL_MASK=66 timeout 300 python tools/trace_step.py > $O/timeline66.txt 2>&1; tail -4 $O/timeline66.txt
 echo "== ncu TS kernel M=32 28672x4096"
-timeout 600 ncu --set full --clock-control none --import-source on -k regex:k_w4a16_ts -s 3 -c 1 -o $O/ts_m32 -f python tools/tc_bench.py --one 28672 4096 32 > $O/ncu_ts.log 2>&1; tail -2 $O/ncu_ts.log; ls -la $O/*.ncu-rep
+timeout 600 ncu --set full --clock-control none -k regex:k_w4a16_ts -s 3 -c 1 -o $O/ts_m32 -f python tools/tc_bench.py --one 28672 4096 32 > $O/ncu_ts.log 2>&1; tail -2 $O/ncu_ts.log; ls -la $O/*.ncu-rep

@@ -19,7 +19,7 @@ echo "== bench $extra"; timeout 900 python bench.py --steps 32 --warmup 4 --no-c
 done
 echo "== bench llama-3.1-70b N=1"; timeout 1200 python bench.py --model llama-3.1-70b --steps 16 --warmup 3 --no-cpu-baseline --no-extras --requests 0 2>$O/bench_70b.err | tee $O/bench_70b.json | python -c "$summ"; tail -2 $O/bench_70b.err
 echo "== ncu full: tcgen05 kernel 28672x4096 M=32"
-timeout 600 ncu --set full --clock-control none --import-source on -k regex:k_w4a16_ts -s 3 -c 1 -o $O/ts_m32 -f python tools/tc_bench.py --one 28672 4096 32 > $O/ncu_ts.log 2>&1; tail -1 $O/ncu_ts.log
+timeout 600 ncu --set full --clock-control none -k regex:k_w4a16_ts -s 3 -c 1 -o $O/ts_m32 -f python tools/tc_bench.py --one 28672 4096 32 > $O/ncu_ts.log 2>&1; tail -1 $O/ncu_ts.log
 echo "== ncu launch list, batch 1"
 timeout 900 ncu --metrics gpu__time_duration.sum --clock-control none -s 1500 -c 600 --csv --log-file $O/launches_b1.csv python bench.py --steps 2 --warmup 3 --no-cpu-baseline --no-extras --requests 0 --prompt 2 > $O/ncu_b1.log 2>&1; python tools/ncu_launch_summary.py $O/launches_b1.csv 2>&1 | head -14
 echo "== tc bench (graph)"; timeout 600 python tools/tc_bench.py --graph > $O/tc_bench.jsonl 2>/dev/null; python - <<PY
