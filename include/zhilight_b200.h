@@ -397,6 +397,93 @@ int zl_llama_stats(zl_llama_t* m, int B, double* weight_bytes, int* kernels_per_
  * Returns total milliseconds, the number of GEMM launches and their algorithmic bytes. */
 int zl_llama_bench_gemms(zl_llama_t* m, int B, int iters, float* ms, int* launches, double* bytes);
 
+/* ------------------------------------------------------------------------------------------ *
+ * Building blocks of layers with an fp32 residual stream, grouped norms, short convolutions and latent attention
+ * ------------------------------------------------------------------------------------------ */
+enum { ZL_GEMM_EPI_NONE = 0, ZL_GEMM_EPI_RELU2 = 1 /* max(v,0)^2 */, ZL_GEMM_EPI_SIGMOID_GATE = 2 /* v * sigmoid(gate) */ };
+/* y[b](M,N) = epi(x[b](M,K) @ w[b](N,K)^T), b < batch, element strides per batch entry; any M, N, K.  in_dtype
+ * ZL_F16 / ZL_BF16 (tensor cores, fp32 accumulation) or ZL_F32 (plain fp32 FMAs, no reduced-precision mode);
+ * out_dtype = in_dtype or ZL_F32; gate (fp32, same indexing as y with ldg / gate_batch_stride) for the gate epilogue. */
+int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride, const void* w, long long ldw,
+               long long w_batch_stride, void* y, long long ldy, long long y_batch_stride, int M, int N, int K, int batch,
+               int in_dtype, int out_dtype, int epilogue, const float* gate, long long ldg, long long gate_batch_stride,
+               int pdl, zl_stream_t stream);
+/* y[t] = w * x[t] / sqrt(mean(x[t]^2 over each of `groups` equal consecutive parts) + eps); x fp32, y out_dtype. */
+int zl_group_rmsnorm(const float* x, long long ldx, const float* weight, void* y, long long ldy, int T, int D, int groups,
+                     float eps, int out_dtype, int pdl, zl_stream_t stream);
+/* x[t] += the same norm of y[t] (fp32).  With ring != NULL also stores conv_in[t] into the convolution ring
+ * ring[slot[t]][pos[t] % (taps-1)][D] for the rows that are among the last taps-1 of their sequence in this step. */
+int zl_group_rmsnorm_residual(const float* y, long long ldy, const float* weight, float* x, long long ldx, int T, int D,
+                              int groups, float eps, const float* conv_in, long long ld_conv_in, const int32_t* slot,
+                              const int32_t* pos, float* ring, int taps, int pdl, zl_stream_t stream);
+/* u[t] = h[t] + sum_j taps_weight[c][j] * h(pos[t] - taps + 1 + j): per-channel causal convolution over the positions of
+ * a sequence; earlier inputs come from this step's rows (rows of a sequence are consecutive) or from the slot's ring,
+ * zeros before position 0.  taps_weight fp32 (D, taps). */
+int zl_causal_conv_mix(const float* h, long long ldh, const float* taps_weight, const int32_t* slot, const int32_t* pos,
+                       const float* ring, void* u, long long ldu, int T, int D, int taps, int out_dtype, int pdl,
+                       zl_stream_t stream);
+/* plain RMS norms of the two low-rank latents inside a fused projection row: proj[t][q_off .. +q_rank) -> cq (T, q_rank)
+ * and, when kv_weight != NULL, proj[t][c_off .. +kv_rank) -> row pos[t] of the latent cache of slot[t]. */
+int zl_latent_norm_append(const float* proj, long long ldp, int q_off, int q_rank, const float* q_weight, void* cq, int c_off,
+                          int kv_rank, const float* kv_weight, void* const* slot_addrs, const int32_t* slot,
+                          const int32_t* pos, int T, float eps, int dtype, int pdl, zl_stream_t stream);
+/* Absorbed attention over cached latents with a softmax sink.  q_absorbed (T, heads, kv_rank) fp32 = W_uk,h^T q_h;
+ * token t sees rows 0..pos[t] of slot_addrs[slot[t]] ((max_seq, kv_rank) of `dtype`); out (T, heads, kv_rank) of `dtype`
+ * = sum_j softmax_with_sink(scale * q_absorbed . c_j) c_j; the denominator holds exp(sink[h]) once.  splits > 1 cuts
+ * every token's keys over that many CTAs (workspace of zl_latent_attention_workspace_bytes). */
+size_t zl_latent_attention_workspace_bytes(int T, int heads, int kv_rank, int splits);
+int zl_latent_attention_prepare(int heads, int kv_rank, int dtype);
+int zl_latent_attention_splits(int T, int heads, int kv_rank, int max_len);
+int zl_latent_attention(const float* q_absorbed, void* const* slot_addrs, const int32_t* slot, const int32_t* pos,
+                        const float* sink, float scale, void* out, int T, int heads, int kv_rank, int splits, void* workspace,
+                        size_t workspace_bytes, int dtype, int pdl, zl_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ *
+ * Dekipel: decoder-only model of latent-attention layers (queries and key-values through low-rank latents, no
+ * positional rotation, causal softmax with a per-head sink, sigmoid output gate, optional sharing of another layer's
+ * latent cache), each sublayer between a pre- and a post-norm (RMS norm in groups), reading its input through a short
+ * causal convolution, with a relu^2 feed-forward.  Same driver shape as zl_llama_*: task slots with per-slot caches,
+ * host (token, slot, position) in, logits / greedy picks out.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct zl_dekipel zl_dekipel_t;
+typedef struct zl_dekipel_layer {
+    int heads, dim, vdim, q_rank, kv_rank;
+    int kv_from; /* -1: own key-value latents; j: reads layer j's latent cache */
+    int ff;      /* 0: no feed-forward sublayer */
+    float scale;
+} zl_dekipel_layer_t;
+typedef struct zl_dekipel_config {
+    int num_layers, width, vocab;
+    int norm_groups, canon_taps;
+    float eps;
+    int dtype; /* ZL_BF16: 16-bit Linears with fp32 accumulation; ZL_F32: everything in fp32 */
+    int max_batch /* slots */, max_seq /* rows per slot */, max_step_tokens /* tokens per step */;
+    int use_pdl, use_graph;
+} zl_dekipel_config_t;
+
+int zl_dekipel_create(const zl_dekipel_config_t* cfg, const zl_dekipel_layer_t* layers, zl_dekipel_t** out);
+void zl_dekipel_destroy(zl_dekipel_t* m);
+/* Stage one checkpoint tensor (HOST pointer, row-major (rows, cols); elem_bytes 2 = bfloat16, 4 = float32 / int32). */
+int zl_dekipel_load_tensor(zl_dekipel_t* m, const char* name, const void* data_host, int rows, int cols, int elem_bytes);
+int zl_dekipel_init_synthetic(zl_dekipel_t* m, uint64_t seed);
+int zl_dekipel_finalize(zl_dekipel_t* m);
+/* One step over T tokens: token t belongs to slot slots[t] at position positions[t]; the rows of one slot are consecutive
+ * with consecutive positions (a prompt portion), or every row is another slot (a decode batch), or any mix.  Appends to
+ * the slots' caches and states.  want_rows (n_want indices into the step's rows): their logits go to logits_host
+ * (n_want, vocab) fp32 and their greedy picks to next_host (n_want); either may be NULL.  Synchronous. */
+int zl_dekipel_step(zl_dekipel_t* m, const int32_t* tokens_host, const int32_t* slots_host, const int32_t* positions_host,
+                    int T, const int32_t* want_rows_host, int n_want, float* logits_host, int32_t* next_host);
+/* Device-resident decode loop (bench): set the (token, position) of slots 0..B-1 once, then every call runs one step,
+ * feeds the greedy picks back and advances the positions on the device; no host sync. */
+int zl_dekipel_set_state(zl_dekipel_t* m, const int32_t* tokens_host, const int32_t* positions_host, int B);
+int zl_dekipel_step_device(zl_dekipel_t* m, int B);
+int zl_dekipel_sync(zl_dekipel_t* m);
+zl_stream_t zl_dekipel_stream(zl_dekipel_t* m);
+/* residual stream after every layer of the last step, (num_layers, T, width) fp32, when capture was switched on */
+int zl_dekipel_capture_layers(zl_dekipel_t* m, int on);
+int zl_dekipel_read_layers(zl_dekipel_t* m, float* out_host, int T);
+int zl_dekipel_stats(zl_dekipel_t* m, double* weight_bytes, int* kernels_per_step);
+
 #ifdef __cplusplus
 }
 #endif

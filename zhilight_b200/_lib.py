@@ -86,6 +86,9 @@ def parse_header(path=HEADER):
     src = re.sub(r"//[^\n]*", " ", src)
     src = re.sub(r"typedef struct zl_llama_config \{.*?\} zl_llama_config_t;", " ", src, flags=re.S)
     src = re.sub(r"typedef struct zl_w4_fused_args \{.*?\} zl_w4_fused_args_t;", " ", src, flags=re.S)
+    src = re.sub(r"typedef struct zl_dekipel_layer \{.*?\} zl_dekipel_layer_t;", " ", src, flags=re.S)
+    src = re.sub(r"typedef struct zl_dekipel_config \{.*?\} zl_dekipel_config_t;", " ", src, flags=re.S)
+    src = re.sub(r"enum \{.*?\};", " ", src, flags=re.S)
     protos = {}
     for m in re.finditer(r"([A-Za-z_][\w \*]*?)\b(zl_\w+)\s*\(([^;{}]*?)\)\s*;", src):
         ret, name, args = m.group(1).strip(), m.group(2), m.group(3).strip()

@@ -1,0 +1,254 @@
+// General tiled GEMM y[b](M,N) = epi(x[b](M,K) @ w[b](N,K)^T) for any M, N, K, with a batch of strided problems
+// (one per attention head) and small fused epilogues.
+//
+// The decode-sized dense Linear of the framework (dense_gemm.cu) wants K % 32 == 0 and M <= 32 per pass and re-streams
+// the weights for every 32 rows; models whose projection ranks are not multiples of 32, prompt-sized M, and per-head
+// weight blocks go through this kernel instead.  16-bit inputs: 64 x 64 x 32 tiles, mma.sync.m16n8k16 with fp32
+// accumulation, register-prefetched double buffering.  fp32 inputs: 64 x 64 x 16 tiles of plain FMAs (no TF32), every
+// product and sum in IEEE fp32.
+#include "common.cuh"
+
+namespace zl {
+
+struct GemmP {
+    const void* x;
+    const void* w;
+    void* y;
+    const float* gate;
+    long long ldx, xb, ldw, wb, ldy, yb, ldg, gb;
+    int M, N, K;
+};
+
+template <int EPI>
+__device__ __forceinline__ float gemm_epilogue(float v, const GemmP& p, int b, int m, int n) {
+    if constexpr (EPI == ZL_GEMM_EPI_RELU2) {
+        const float r = fmaxf(v, 0.f);
+        return r * r;
+    } else if constexpr (EPI == ZL_GEMM_EPI_SIGMOID_GATE) {
+        const float g = p.gate[(size_t)b * p.gb + (size_t)m * p.ldg + n];
+        return v * (1.0f / (1.0f + expf(-g)));
+    } else {
+        return v;
+    }
+}
+
+// ---- 16-bit inputs -------------------------------------------------------------------------------------------------
+constexpr int kGB = 64, kGK = 32, kGPad = 8;
+
+template <typename T>
+__device__ __forceinline__ uint4 load8(const T* base, long long ld, int row, int rows, int k, int K, bool vec) {
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (row >= rows || k >= K) return r;
+    const T* p = base + (size_t)row * ld + k;
+    if (vec) return *reinterpret_cast<const uint4*>(p);   // vec implies K % 8 == 0: the 8 elements are inside the row
+    T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (k + i < K) e[i] = p[i];
+    return r;
+}
+
+template <typename T>
+__device__ __forceinline__ void mma_in(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_in<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    mma_16816_f16(d, a, b0, b1, d);
+}
+template <>
+__device__ __forceinline__ void mma_in<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    mma_16816_bf16(d, a, b0, b1, d);
+}
+
+template <typename T, typename TO, int EPI>
+__global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w) {
+    __shared__ __align__(16) T sA[2][kGB][kGK + kGPad];
+    __shared__ __align__(16) T sB[2][kGB][kGK + kGPad];
+    pdl_trigger();
+    const int b = blockIdx.z;
+    const T* x = static_cast<const T*>(p.x) + (size_t)b * p.xb;
+    const T* w = static_cast<const T*>(p.w) + (size_t)b * p.wb;
+    const int m0 = blockIdx.y * kGB, n0 = blockIdx.x * kGB;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int lr = tid >> 2, lc = (tid & 3) * 8;   // this thread's 8-element pieces: rows lr and lr + 32
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+
+    uint4 rw[2], rx[2];
+    rw[0] = load8(w, p.ldw, n0 + lr, p.N, lc, p.K, vec_w);        // weights do not depend on the predecessor kernel
+    rw[1] = load8(w, p.ldw, n0 + lr + 32, p.N, lc, p.K, vec_w);
+    pdl_wait();
+    rx[0] = load8(x, p.ldx, m0 + lr, p.M, lc, p.K, vec_x);
+    rx[1] = load8(x, p.ldx, m0 + lr + 32, p.M, lc, p.K, vec_x);
+    const int steps = cdiv(p.K, kGK);
+    for (int s = 0; s < steps; ++s) {
+        const int buf = s & 1;
+        *reinterpret_cast<uint4*>(&sA[buf][lr][lc]) = rx[0];
+        *reinterpret_cast<uint4*>(&sA[buf][lr + 32][lc]) = rx[1];
+        *reinterpret_cast<uint4*>(&sB[buf][lr][lc]) = rw[0];
+        *reinterpret_cast<uint4*>(&sB[buf][lr + 32][lc]) = rw[1];
+        __syncthreads();   // one barrier per step: buffer `buf` is next written two steps later, after the next barrier
+        if (s + 1 < steps) {
+            const int k = (s + 1) * kGK + lc;
+            rx[0] = load8(x, p.ldx, m0 + lr, p.M, k, p.K, vec_x);
+            rx[1] = load8(x, p.ldx, m0 + lr + 32, p.M, k, p.K, vec_x);
+            rw[0] = load8(w, p.ldw, n0 + lr, p.N, k, p.K, vec_w);
+            rw[1] = load8(w, p.ldw, n0 + lr + 32, p.N, k, p.K, vec_w);
+        }
+#pragma unroll
+        for (int kk = 0; kk < kGK; kk += 16) {
+            uint32_t a[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm + i * 16 + g;
+                a[i][0] = *reinterpret_cast<const uint32_t*>(&sA[buf][r][kk + 2 * t]);
+                a[i][1] = *reinterpret_cast<const uint32_t*>(&sA[buf][r + 8][kk + 2 * t]);
+                a[i][2] = *reinterpret_cast<const uint32_t*>(&sA[buf][r][kk + 2 * t + 8]);
+                a[i][3] = *reinterpret_cast<const uint32_t*>(&sA[buf][r + 8][kk + 2 * t + 8]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = wn + j * 8 + g;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sB[buf][c][kk + 2 * t]);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sB[buf][c][kk + 2 * t + 8]);
+                mma_in<T>(acc[0][j], a[0], b0, b1);
+                mma_in<T>(acc[1][j], a[1], b0, b1);
+            }
+        }
+    }
+    TO* y = static_cast<TO*>(p.y) + (size_t)b * p.yb;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int m = m0 + wm + i * 16 + g + ((c >> 1) ? 8 : 0);
+                const int n = n0 + wn + j * 8 + 2 * t + (c & 1);
+                if (m < p.M && n < p.N) y[(size_t)m * p.ldy + n] = from_f32<TO>(gemm_epilogue<EPI>(acc[i][j][c], p, b, m, n));
+            }
+}
+
+// ---- fp32 inputs ---------------------------------------------------------------------------------------------------
+constexpr int kFK = 16;
+
+__device__ __forceinline__ float4 load4f(const float* base, long long ld, int row, int rows, int k, int K, bool vec) {
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row >= rows || k >= K) return r;
+    const float* p = base + (size_t)row * ld + k;
+    if (vec) return *reinterpret_cast<const float4*>(p);
+    r.x = p[0];
+    if (k + 1 < K) r.y = p[1];
+    if (k + 2 < K) r.z = p[2];
+    if (k + 3 < K) r.w = p[3];
+    return r;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(256) k_gemm_f32(GemmP p, int vec_x, int vec_w) {
+    __shared__ float sA[kFK][kGB + 4];   // k-major: the inner product walks k, 4 rows / columns per thread
+    __shared__ float sB[kFK][kGB + 4];
+    pdl_trigger();
+    const int b = blockIdx.z;
+    const float* x = static_cast<const float*>(p.x) + (size_t)b * p.xb;
+    const float* w = static_cast<const float*>(p.w) + (size_t)b * p.wb;
+    const int m0 = blockIdx.y * kGB, n0 = blockIdx.x * kGB;
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int lr = tid >> 2, lc = (tid & 3) * 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    float4 rw = load4f(w, p.ldw, n0 + lr, p.N, lc, p.K, vec_w);
+    pdl_wait();
+    float4 rx = load4f(x, p.ldx, m0 + lr, p.M, lc, p.K, vec_x);
+    const int steps = cdiv(p.K, kFK);
+    for (int s = 0; s < steps; ++s) {
+        __syncthreads();   // the previous step's reads are done
+        sA[lc + 0][lr] = rx.x, sA[lc + 1][lr] = rx.y, sA[lc + 2][lr] = rx.z, sA[lc + 3][lr] = rx.w;
+        sB[lc + 0][lr] = rw.x, sB[lc + 1][lr] = rw.y, sB[lc + 2][lr] = rw.z, sB[lc + 3][lr] = rw.w;
+        __syncthreads();
+        if (s + 1 < steps) {
+            const int k = (s + 1) * kFK + lc;
+            rx = load4f(x, p.ldx, m0 + lr, p.M, k, p.K, vec_x);
+            rw = load4f(w, p.ldw, n0 + lr, p.N, k, p.K, vec_w);
+        }
+#pragma unroll
+        for (int k = 0; k < kFK; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&sA[k][ty * 4]);
+            const float4 bb = *reinterpret_cast<const float4*>(&sB[k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+    }
+    float* y = static_cast<float*>(p.y) + (size_t)b * p.yb;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < p.M && n < p.N) y[(size_t)m * p.ldy + n] = gemm_epilogue<EPI>(acc[i][j], p, b, m, n);
+        }
+}
+
+template <typename T, typename TO>
+static cudaError_t launch_mma(const GemmP& p, int batch, int epi, bool vx, bool vw, bool pdl, cudaStream_t st) {
+    const dim3 grid(cdiv(p.N, kGB), cdiv(p.M, kGB), batch), block(128);
+    if (epi == ZL_GEMM_EPI_RELU2) return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_RELU2>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+    if (epi == ZL_GEMM_EPI_SIGMOID_GATE)
+        return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_SIGMOID_GATE>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+    return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_NONE>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+}
+
+static bool aligned_for(const void* ptr, long long ld, long long bstride, int K, int elem, int batch) {
+    const int per16 = 16 / elem;
+    return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && ld % per16 == 0 && K % per16 == 0 &&
+           (batch == 1 || bstride % per16 == 0);
+}
+
+}  // namespace zl
+
+using namespace zl;
+
+extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride, const void* w, long long ldw,
+                          long long w_batch_stride, void* y, long long ldy, long long y_batch_stride, int M, int N, int K,
+                          int batch, int in_dtype, int out_dtype, int epilogue, const float* gate, long long ldg,
+                          long long gate_batch_stride, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(x && w && y && M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535);
+    ZL_CHECK_ARG(ldx >= K && ldw >= K && ldy >= N);
+    ZL_CHECK_ARG(in_dtype == ZL_F16 || in_dtype == ZL_BF16 || in_dtype == ZL_F32);
+    ZL_CHECK_ARG(out_dtype == in_dtype || out_dtype == ZL_F32);
+    ZL_CHECK_ARG(epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_RELU2 || epilogue == ZL_GEMM_EPI_SIGMOID_GATE);
+    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_SIGMOID_GATE || (gate && ldg >= N));
+    ZL_CHECK_ARG(cdiv(M, kGB) <= 65535);
+    GemmP p{x, w, y, gate, ldx, x_batch_stride, ldw, w_batch_stride, ldy, y_batch_stride, ldg, gate_batch_stride, M, N, K};
+    const int elem = in_dtype == ZL_F32 ? 4 : 2;
+    const bool vx = aligned_for(x, ldx, x_batch_stride, K, elem, batch), vw = aligned_for(w, ldw, w_batch_stride, K, elem, batch);
+    cudaError_t e;
+    if (in_dtype == ZL_F32) {
+        const dim3 grid(cdiv(N, kGB), cdiv(M, kGB), batch), block(256);
+        if (epilogue == ZL_GEMM_EPI_RELU2)
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_RELU2>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+        else if (epilogue == ZL_GEMM_EPI_SIGMOID_GATE)
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_SIGMOID_GATE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+        else
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_NONE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+    } else if (in_dtype == ZL_BF16) {
+        e = out_dtype == ZL_F32 ? launch_mma<__nv_bfloat16, float>(p, batch, epilogue, vx, vw, pdl != 0, stream)
+                                : launch_mma<__nv_bfloat16, __nv_bfloat16>(p, batch, epilogue, vx, vw, pdl != 0, stream);
+    } else {
+        e = out_dtype == ZL_F32 ? launch_mma<__half, float>(p, batch, epilogue, vx, vw, pdl != 0, stream)
+                                : launch_mma<__half, __half>(p, batch, epilogue, vx, vw, pdl != 0, stream);
+    }
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}

@@ -6,7 +6,7 @@
 // Int4GPTQ load pipeline (src/nn/linear/linear.cpp:1139-1244).  The reference launches ~12 kernels per
 // layer with no graph; here a layer is 8 launches chained with programmatic dependent launch inside one
 // CUDA graph per batch size.
-#include "common.cuh"
+#include "runner_common.cuh"
 #include "w4_layout.cuh"
 #include "comm_dev.cuh"
 
@@ -21,10 +21,8 @@ extern unsigned long long* g_w4_trace;   // debug timeline buffer (zl_w4_set_tra
 
 namespace {
 
-struct Staged {
-    void* ptr = nullptr;
-    int rows = 0, cols = 0, elem = 0;
-};
+using zl::Staged;
+using zl::SlotCache;
 
 struct W4Lin {
     void* packed = nullptr;     // ZLW4  (fp16 HMMA kernels) -- only kept when some batch size needs it
@@ -47,9 +45,8 @@ struct Layer {
     void* ln_ff = nullptr;
     W4Lin q_qkv, q_o, q_gu, q_down;
     DenseLin d_qkv, d_o, d_gu, d_down;
-    void* kbuf = nullptr;   // (max_batch, max_seq, Hkv, d)
-    void* vbuf = nullptr;
-    void** k_addrs = nullptr;   // device (max_batch)
+    SlotCache kcache, vcache;   // (max_batch, max_seq, Hkv, d) each
+    void** k_addrs = nullptr;   // = kcache.addrs: device (max_batch)
     void** v_addrs = nullptr;
 };
 
@@ -58,7 +55,7 @@ struct Layer {
 struct zl_llama {
     zl_llama_config_t cfg{};
     cudaStream_t stream = nullptr;
-    std::map<std::string, Staged> staged;
+    zl::StagedMap staged;
     std::vector<Layer> layers;
     void* emb = nullptr;
     void* lm_head = nullptr;
@@ -115,18 +112,6 @@ namespace {
 
 using namespace zl;
 
-#define RCHECK(expr)                \
-    do {                            \
-        int _rc = (expr);           \
-        if (_rc != ZL_OK) return _rc; \
-    } while (0)
-
-
-
-int dmalloc(void** p, size_t bytes) {
-    ZL_CHECK_CUDA(cudaMalloc(p, bytes ? bytes : 16));
-    return ZL_OK;
-}
 
 __global__ void k_lens_from_pos(const int32_t* __restrict__ pos, int32_t* __restrict__ lens, int B,
                                 unsigned long long* trace) {
@@ -193,10 +178,6 @@ __global__ void k_iota(int32_t* p, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = i;
 }
-__global__ void k_ptr_table(void** tab, char* base, size_t stride, int n) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) tab[i] = base + (size_t)i * stride;
-}
 __global__ void k_swiglu_row_map(int32_t* map, int F) {
     // packed row p: 16-row tile = 8 gate rows then the 8 matching up rows (source = [gate(F); up(F)])
     int p = blockIdx.x * blockDim.x + threadIdx.x;
@@ -206,32 +187,9 @@ __global__ void k_swiglu_row_map(int32_t* map, int F) {
     }
 }
 
-const Staged* find(const zl_llama* m, const std::string& name) {
-    auto it = m->staged.find(name);
-    return it == m->staged.end() ? nullptr : &it->second;
-}
+const Staged* find(const zl_llama* m, const std::string& name) { return staged_find(m->staged, name); }
 
-void drop(zl_llama* m, const std::string& name) {
-    auto it = m->staged.find(name);
-    if (it != m->staged.end()) {
-        cudaFree(it->second.ptr);
-        m->staged.erase(it);
-    }
-}
-
-// frees device temporaries on every exit path of a load helper
-struct DevTmp {
-    std::vector<void*> ptrs;
-    ~DevTmp() {
-        for (void* p : ptrs)
-            if (p) cudaFree(p);
-    }
-    int alloc(void** p, size_t bytes) {
-        int rc = dmalloc(p, bytes);
-        if (rc == ZL_OK) ptrs.push_back(*p);
-        return rc;
-    }
-};
+void drop(zl_llama* m, const std::string& name) { staged_drop(m->staged, name); }
 
 int fail_state(int line, const std::string& msg, int code = ZL_ERR_STATE) {
     zl_set_last_error(__FILE__, line, msg.c_str());
@@ -558,17 +516,12 @@ int alloc_runtime(zl_llama* m) {
     const int B = c.max_batch, D = c.dim_model, d = c.dim_head;
     const size_t kv_task = (size_t)c.max_seq * m->hkv * d * 2;
     for (auto& L : m->layers) {
-        RCHECK(dmalloc(&L.kbuf, kv_task * B));
-        RCHECK(dmalloc(&L.vbuf, kv_task * B));
-        // never-written rows must be finite: masked keys still multiply their V rows by an exact 0, and with the
+        // never-written rows are zero: masked keys still multiply their V rows by an exact 0, and with the
         // dual-stream prefill one half's attention sees the other half's rows before they are appended
-        ZL_CHECK_CUDA(cudaMemsetAsync(L.kbuf, 0, kv_task * B, m->stream));
-        ZL_CHECK_CUDA(cudaMemsetAsync(L.vbuf, 0, kv_task * B, m->stream));
-        RCHECK(dmalloc((void**)&L.k_addrs, sizeof(void*) * B));
-        RCHECK(dmalloc((void**)&L.v_addrs, sizeof(void*) * B));
-        k_ptr_table<<<cdiv(B, 256), 256, 0, m->stream>>>(L.k_addrs, (char*)L.kbuf, kv_task, B);
-        k_ptr_table<<<cdiv(B, 256), 256, 0, m->stream>>>(L.v_addrs, (char*)L.vbuf, kv_task, B);
-        ZL_CHECK_LAUNCH();
+        RCHECK(L.kcache.create(B, kv_task, m->stream));
+        RCHECK(L.vcache.create(B, kv_task, m->stream));
+        L.k_addrs = L.kcache.addrs;
+        L.v_addrs = L.vcache.addrs;
     }
     const int T = c.prefill_chunk > B ? c.prefill_chunk : B;   // tokens per launch: decode batch or prefill chunk
     m->tok_cap = T;
@@ -1130,8 +1083,10 @@ extern "C" void zl_llama_destroy(zl_llama_t* m) {
     for (auto& L : m->layers) {
         for (void* p : {L.ln_attn, L.ln_ff, L.q_qkv.packed, L.q_qkv.bias, L.q_o.packed, L.q_o.bias, L.q_gu.packed,
                         L.q_down.packed, L.q_down.bias, L.q_qkv.packed_i, L.q_o.packed_i, L.q_gu.packed_i, L.q_down.packed_i, L.d_qkv.w, L.d_qkv.bias, L.d_o.w, L.d_o.bias, L.d_gu.w,
-                        L.d_gu.bias, L.d_down.w, L.d_down.bias, L.d_qkv.w8, L.d_qkv.w_scale, L.d_o.w8, L.d_o.w_scale, L.d_gu.w8, L.d_gu.w_scale, L.d_down.w8, L.d_down.w_scale, L.kbuf, L.vbuf, (void*)L.k_addrs, (void*)L.v_addrs})
+                        L.d_gu.bias, L.d_down.w, L.d_down.bias, L.d_qkv.w8, L.d_qkv.w_scale, L.d_o.w8, L.d_o.w_scale, L.d_gu.w8, L.d_gu.w_scale, L.d_down.w8, L.d_down.w_scale})
             if (p) cudaFree(p);
+        L.kcache.destroy();
+        L.vcache.destroy();
     }
     for (void* p : {m->emb, m->lm_head_tied ? nullptr : m->lm_head, m->ln_f, m->h, m->xn, m->qkv, m->q, m->ao, m->act,
                     m->pend, m->gu, (void*)m->logits, (void*)m->cosb, (void*)m->sinb, (void*)m->d_tokens,
@@ -1161,17 +1116,7 @@ extern "C" int zl_llama_load_tensor(zl_llama_t* m, const char* name, const void*
         zl_set_last_error(__FILE__, __LINE__, "model already finalized");
         return ZL_ERR_STATE;
     }
-    Staged s;
-    s.rows = rows;
-    s.cols = cols;
-    s.elem = elem_bytes;
-    const size_t bytes = (size_t)rows * cols * elem_bytes;
-    RCHECK(dmalloc(&s.ptr, bytes));
-    ZL_CHECK_CUDA(cudaMemcpyAsync(s.ptr, data_host, bytes, cudaMemcpyHostToDevice, m->stream));
-    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
-    drop(m, name);
-    m->staged[name] = s;
-    return ZL_OK;
+    return staged_load(m->staged, name, data_host, rows, cols, elem_bytes, m->stream);
 }
 
 extern "C" int zl_llama_finalize(zl_llama_t* m) {
