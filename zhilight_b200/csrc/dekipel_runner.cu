@@ -227,6 +227,13 @@ int finalize_layer(zl_dekipel* m, int l) {
     return ZL_OK;
 }
 
+// attention split counts are baked into a graph: one graph per length bucket
+int len_bucket(const zl_dekipel* m, int max_len) {
+    int b = 256;
+    while (b < max_len) b <<= 1;
+    return b < m->cfg.max_seq ? b : (m->cfg.max_seq > 256 ? m->cfg.max_seq : 256);
+}
+
 int alloc_runtime(zl_dekipel* m) {
     const auto& c = m->cfg;
     const int D = c.width, T = m->tcap, B = c.max_batch, keep = c.canon_taps - 1;
@@ -248,9 +255,10 @@ int alloc_runtime(zl_dekipel* m) {
         hr = std::max(hr, (size_t)lc.heads * lc.kv_rank);
         hv = std::max(hv, (size_t)lc.heads * lc.vdim);
         ff = std::max(ff, (size_t)lc.ff);
-        for (int b = 1; b <= B; ++b) {
-            const int s = zl_latent_attention_splits(b, lc.heads, lc.kv_rank, c.max_seq);
+        for (int b = 1; b <= T; ++b) {   // the split count falls as the rows grow: size for the worst product
+            const int s = zl_latent_attention_splits(b, lc.heads, lc.kv_rank, len_bucket(m, c.max_seq));
             m->attn_ws_bytes = std::max(m->attn_ws_bytes, zl_latent_attention_workspace_bytes(b, lc.heads, lc.kv_rank, s));
+            if (s == 1) break;
         }
     }
     for (auto& L : m->layers)
@@ -317,7 +325,7 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
         RCHECK(linear(m, m->cq, lc.q_rank, L.uq, H * lc.dim, m->q, T, dt, ZL_GEMM_EPI_NONE));
         RCHECK(zl_gemm_nt(m->q, (long long)H * lc.dim, lc.dim, L.uk_t, lc.dim, (long long)R * lc.dim, m->qa, (long long)H * R, R,
                           T, R, lc.dim, H, dt, ZL_F32, ZL_GEMM_EPI_NONE, nullptr, 0, 0, pdl, st));
-        const int splits = T <= c.max_batch ? zl_latent_attention_splits(T, H, R, max_len) : 1;
+        const int splits = zl_latent_attention_splits(T, H, R, max_len);
         RCHECK(zl_latent_attention(m->qa, L.lat_addrs, m->d_slots, m->d_pos, L.sink, lc.scale, m->olat, T, H, R, splits,
                                    m->attn_ws, m->attn_ws_bytes, dt, pdl, st));
         RCHECK(zl_gemm_nt(m->olat, (long long)H * R, R, L.uv, R, (long long)lc.vdim * R, m->og, (long long)H * lc.vdim, lc.vdim, T,
@@ -347,12 +355,6 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
         RCHECK(zl_argmax(m->logits, m->d_next, n_want, c.vocab, m->argmax_ws, zl_argmax_workspace_bytes(n_want), pdl, st));
     }
     return ZL_OK;
-}
-
-int len_bucket(const zl_dekipel* m, int max_len) {
-    int b = 256;
-    while (b < max_len) b <<= 1;
-    return b < m->cfg.max_seq ? b : (m->cfg.max_seq > 256 ? m->cfg.max_seq : 256);
 }
 
 // decode-sized steps replay a CUDA graph per (rows, wanted rows, length bucket); prompt portions are enqueued directly

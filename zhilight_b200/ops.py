@@ -392,3 +392,76 @@ def argmax(logits):
     ws = torch.empty(nb, dtype=torch.uint8, device=logits.device)
     _lib.call("zl_argmax", _p(logits), _p(out), t, v, _p(ws), nb, 0, _stream())
     return out
+
+
+# ------------------------------------------------------------------ fp32-residual layers: grouped norm, conv, latents
+GEMM_EPI_NONE, GEMM_EPI_RELU2, GEMM_EPI_SIGMOID_GATE = 0, 1, 2
+
+
+def gemm_nt(x, w, out_dtype=None, epilogue=GEMM_EPI_NONE, gate=None):
+    """y = epi(x @ w^T).  x (M, K) with w (N, K), or batched x (B, M, K) with w (B, N, K); any sizes.  gate (fp32, shape of
+    y) for GEMM_EPI_SIGMOID_GATE."""
+    batched = x.dim() == 3
+    xb, wb = (x, w) if batched else (x[None], w[None])
+    b, m, k = xb.shape
+    n = wb.shape[1]
+    od = out_dtype or x.dtype
+    y = torch.empty((b, m, n), dtype=od, device=x.device)
+    _lib.call("zl_gemm_nt", _p(xb), k, m * k, _p(wb), k, n * k, _p(y), n, m * n, m, n, k, b, _dt(x), _dt(y), epilogue,
+              _p(gate), n, m * n, 0, _stream())
+    return y if batched else y[0]
+
+
+def group_rmsnorm(x, weight, groups, eps, out_dtype=torch.float32):
+    """x (T, D) fp32, weight (D) fp32 -> (T, D): RMS norm over each of `groups` equal consecutive parts."""
+    t, d = x.shape
+    y = torch.empty((t, d), dtype=out_dtype, device=x.device)
+    _lib.call("zl_group_rmsnorm", _p(x), d, _p(weight), _p(y), d, t, d, groups, eps, _dt(y), 0, _stream())
+    return y
+
+
+def group_rmsnorm_residual(y, weight, x, groups, eps, conv_in=None, slot=None, pos=None, ring=None, taps=1):
+    """x += group_rmsnorm(y) in place; with ring (slots, taps-1, D) also stores conv_in rows into the slots' rings."""
+    t, d = x.shape
+    _lib.call("zl_group_rmsnorm_residual", _p(y), d, _p(weight), _p(x), d, t, d, groups, eps, _p(conv_in), d, _p(slot),
+              _p(pos), _p(ring), taps, 0, _stream())
+    return x
+
+
+def causal_conv_mix(h, taps_weight, slot, pos, ring, out_dtype=torch.float32):
+    """u = h + causal conv of h over each sequence's positions; h (T, D) fp32, taps_weight (D, taps) fp32,
+    ring (slots, taps-1, D) fp32 or None when taps == 1."""
+    t, d = h.shape
+    u = torch.empty((t, d), dtype=out_dtype, device=h.device)
+    _lib.call("zl_causal_conv_mix", _p(h), d, _p(taps_weight), _p(slot), _p(pos), _p(ring), _p(u), d, t, d,
+              taps_weight.shape[1], _dt(u), 0, _stream())
+    return u
+
+
+def slot_table(cache):
+    """cache (slots, rows, width) -> int64 tensor of the slots' base addresses (a device pointer table)."""
+    step = cache.stride(0) * cache.element_size()
+    return torch.tensor([cache.data_ptr() + i * step for i in range(cache.shape[0])], dtype=torch.int64, device=cache.device)
+
+
+def latent_norm_append(proj, q_off, q_weight, c_off, kv_weight, cache, table, slot, pos, eps):
+    """RMS norms of the query latent (-> returned (T, q_rank)) and of the key-value latent (-> cache rows (slot, pos))."""
+    t, ldp = proj.shape
+    q_rank = q_weight.numel()
+    cq = torch.empty((t, q_rank), dtype=cache.dtype, device=proj.device)
+    _lib.call("zl_latent_norm_append", _p(proj), ldp, q_off, q_rank, _p(q_weight), _p(cq), c_off,
+              cache.shape[2], _p(kv_weight), _p(table), _p(slot), _p(pos), t, eps, _dt(cache), 0, _stream())
+    return cq
+
+
+def latent_attention(q_absorbed, cache, table, slot, pos, sink, scale, splits=1):
+    """q_absorbed (T, H, R) fp32, cache (slots, rows, R) -> (T, H, R) of the cache dtype."""
+    t, h, r = q_absorbed.shape
+    lib = _lib.load()
+    _lib.check(lib.zl_latent_attention_prepare(h, r, _dt(cache)))
+    nbytes = lib.zl_latent_attention_workspace_bytes(t, h, r, splits)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=cache.device)
+    out = torch.empty((t, h, r), dtype=cache.dtype, device=cache.device)
+    _lib.call("zl_latent_attention", _p(q_absorbed), _p(table), _p(slot), _p(pos), _p(sink), scale, _p(out), t, h, r, splits,
+              _p(ws), nbytes, _dt(cache), 0, _stream())
+    return out
