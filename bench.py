@@ -329,6 +329,109 @@ def step_bytes_of(cfg, weight_bytes, B, ctx):
     return weight_bytes + B * ctx * cfg["num_layers"] * 2 * cfg["num_kv_heads"] * cfg["dim_head"] * 2
 
 
+# ----------------------------------------------------------------------------------------------------------------------
+# --compare-dekipel: prefill and decode throughput of the Dekipel family beside the bf16 Llama decoder at equal width,
+# depth, heads and (nearly) equal parameter count, random weights.  Does not touch the default workload.
+# ----------------------------------------------------------------------------------------------------------------------
+COMPARE_SIZES = {
+    # width, heads, head dim, layers, vocab, Llama ff; Dekipel: ff = 1.5 x (two matrices instead of three), ranks below
+    "1b-like": dict(width=2048, heads=16, dim=128, layers=4, vocab=32768, ff=8192, q_rank=768, kv_rank=512),
+    "8b-like": dict(width=4096, heads=32, dim=128, layers=4, vocab=32768, ff=14336, q_rank=1536, kv_rank=512),
+}
+
+
+def _dekipel_config(sz):
+    mixer = dict(heads=sz["heads"], dim=sz["dim"], vdim=sz["dim"], q_rank=sz["q_rank"], kv_rank=sz["kv_rank"],
+                 scale=sz["dim"] ** -0.5)
+    layers = []
+    for i in range(sz["layers"]):
+        mx = dict(mixer)
+        if i % 2 == 1:
+            mx["kv_from"] = i - 1           # every second layer reads its neighbour's latents
+        layers.append({"type": "latent_attention", "mixer": mx, "mlp": {"kind": "dense", "ff": sz["ff"] * 3 // 2}})
+    return {"architecture": "Dekipel", "vocab": sz["vocab"], "width": sz["width"], "layers": layers,
+            "norm": {"eps": 1e-5, "groups": 2}, "canon": {"taps": 3}}
+
+
+def _linear_params(kind, sz):
+    D, H, d, ff = sz["width"], sz["heads"], sz["dim"], sz["ff"]
+    if kind == "llama":
+        per = D * (H * d + 2 * 8 * d) + H * d * D + 3 * D * ff
+        return per * sz["layers"] + sz["vocab"] * D
+    q, r = sz["q_rank"], sz["kv_rank"]
+    own = (sz["layers"] + 1) // 2
+    per = D * q + q * H * d + 2 * H * d * r + 2 * H * d * D + 2 * D * (ff * 3 // 2)
+    return per * sz["layers"] + own * D * r + sz["vocab"] * D
+
+
+def run_compare_dekipel(args):
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(0)
+    from zhilight_b200 import build
+    build.build()
+    from zhilight_b200.dekipel import DekipelDecoder
+    from zhilight_b200.llama import LlamaDecoder
+    hbm, how = read_peaks()
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tflops = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
+    ctx, chunk, n_prompt = args.prompt if args.prompt > 128 else 1024, 1024, 2048
+    steps, warm = max(args.steps, 16), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    rows = []
+    for name, sz in COMPARE_SIZES.items():
+        for kind in ("dekipel", "llama"):
+            max_seq = max(ctx, n_prompt) + 4 * (steps + warm) + 64
+            if kind == "dekipel":
+                dec = DekipelDecoder.from_config_dict(_dekipel_config(sz), dtype="bf16", max_batch=32, max_seq=max_seq,
+                                                      max_step_tokens=chunk)
+                cache_row = sz["kv_rank"] * 2 * ((sz["layers"] + 1) // 2)
+            else:
+                dec = LlamaDecoder(num_layers=sz["layers"], dim_model=sz["width"], num_heads=sz["heads"], num_kv_heads=8,
+                                   dim_head=sz["dim"], dim_ff=sz["ff"], vocab_size=sz["vocab"], quant_type=0, dtype="bf16",
+                                   max_batch=32, max_seq=max_seq, prefill_chunk=chunk)
+                cache_row = 2 * 8 * sz["dim"] * 2 * sz["layers"]
+            dec.init_synthetic(seed=1)
+            stream = torch.cuda.ExternalStream(dec.stream())
+            params = _linear_params(kind, sz)
+            out = {"size": name, "model": kind, "linear_params": params}
+            # prefill: n_prompt tokens of one request in chunks of `chunk`; every pass re-reads all weights (> L2)
+            toks = rng.integers(0, sz["vocab"], n_prompt).astype(np.int32)
+            for _ in range(2):
+                dec.prefill(0, toks, 0)
+            t0 = time.perf_counter()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                dec.prefill(0, toks, 0)
+            e1.record(stream)
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / 3
+            flops = 2.0 * (params - sz["vocab"] * sz["width"]) * n_prompt
+            out["prefill"] = {"tokens": n_prompt, "chunk": chunk, "ms": round(ms, 3), "tok_s": round(n_prompt / ms * 1e3),
+                              "linear_tflops": round(flops / ms / 1e9, 1),
+                              "of_measured_bf16_peak": round(flops / ms / 1e9 / tflops, 4)}
+            # decode: every slot filled to ctx rows, then the device-resident loop
+            for b in range(32):
+                dec.prefill(b, toks[:ctx], 0)
+            for B in (1, 32):
+                dec.set_state(rng.integers(0, sz["vocab"], B).astype(np.int32), np.full(B, ctx, dtype=np.int32))
+                ms, _ = measure_decode(dec, B, steps, warm, stream, torch.cuda.synchronize)
+                step_bytes = params * 2 + B * (ctx + warm + steps // 2) * cache_row
+                out["decode_b%d" % B] = {"ctx": ctx, "ms_per_step": round(ms / steps, 4), "tok_s": round(B * steps / ms * 1e3, 1),
+                                          "step_bytes": int(step_bytes),
+                                          "of_%s_hbm_peak" % how: round(step_bytes / (ms / steps * 1e-3) / 1e9 / hbm, 4)}
+            out["kernels_per_step"] = dec.stats()[1] if kind == "dekipel" else dec.stats(1)[1]
+            dec.close()
+            del dec
+            torch.cuda.empty_cache()
+            rows.append(out)
+    print(json.dumps({"compare": "dekipel vs llama (bf16, random weights, synthetic tokens)", "rows": rows,
+                      "timing": "CUDA events on the model's stream; weights per pass larger than L2"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -351,7 +454,12 @@ def main():
                     help="default: the model's BASELINE quantisation (GPTQ int4 for 8B, bf16 for 1B); int8 / fp8: W8A8 Linear rows")
     ap.add_argument("--prefill-chunk", type=int, default=128, help="tokens per chunked-prefill pass of the TTFT measurement")
     ap.add_argument("--fuse", type=int, default=2, help="0: one kernel per reference op; 1: +RMSNorm fused; 2: +qkv RoPE/KV epilogue")
+    ap.add_argument("--compare-dekipel", action="store_true",
+                    help="instead of the default workload: Dekipel beside the bf16 Llama decoder at a few layer sizes")
     args = ap.parse_args()
+    if args.compare_dekipel:
+        run_compare_dekipel(args)
+        return
 
     cfg = model_cfg(args.model)
     quant_name = "bf16" if args.model == "llama-3.2-1b" else "gptq-int4-g128-sym"

@@ -193,6 +193,9 @@ int zl_w8a8_gemm(const void* xq, const float* x_scale, const void* w, const void
  * out_dtype f16/bf16/f32. */
 int zl_dense_gemm_skinny(const void* x, int ldx, const void* w, const void* bias, void* y, int M, int N, int K,
                          int dtype, int out_dtype, int pdl, zl_stream_t stream);
+/* the same with an activation on the output: act 0 none, 1 relu(v)^2 */
+int zl_dense_gemm_skinny_act(const void* x, int ldx, const void* w, const void* bias, void* y, int M, int N, int K, int dtype,
+                             int out_dtype, int act, int pdl, zl_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------ *
  * Norm / residual / activation
@@ -422,6 +425,10 @@ int zl_group_rmsnorm_residual(const float* y, long long ldy, const float* weight
 int zl_causal_conv_mix(const float* h, long long ldh, const float* taps_weight, const int32_t* slot, const int32_t* pos,
                        const float* ring, void* u, long long ldu, int T, int D, int taps, int out_dtype, int pdl,
                        zl_stream_t stream);
+/* zl_group_rmsnorm (-> h, fp32, kept for the ring update) and zl_causal_conv_mix (-> u) in one kernel. */
+int zl_group_norm_conv(const float* x, long long ldx, const float* norm_weight, const float* taps_weight, const int32_t* slot,
+                       const int32_t* pos, const float* ring, float* h, void* u, int T, int D, int groups, int taps, float eps,
+                       int out_dtype, int pdl, zl_stream_t stream);
 /* plain RMS norms of the two low-rank latents inside a fused projection row: proj[t][q_off .. +q_rank) -> cq (T, q_rank)
  * and, when kv_weight != NULL, proj[t][c_off .. +kv_rank) -> row pos[t] of the latent cache of slot[t]. */
 int zl_latent_norm_append(const float* proj, long long ldp, int q_off, int q_rank, const float* q_weight, void* cq, int c_off,

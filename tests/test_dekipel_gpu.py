@@ -128,6 +128,40 @@ def test_causal_conv_with_slot_state(cuda, lib, taps):
     assert at == {1: n, 2: n}
 
 
+@pytest.mark.parametrize("taps,groups", [(1, 1), (2, 3), (3, 2), (4, 6)])
+def test_fused_norm_conv_matches_norm_then_conv(cuda, lib, taps, groups):
+    """The fused pre-norm + convolution kernel over the same plan of mixed portions, rings carried from step to step."""
+    import torch
+    from zhilight_b200 import ops
+    d, n = 36, 19
+    rng = np.random.default_rng(taps * 10 + groups)
+    w, nw = rng.uniform(-1, 1, (d, taps)), rng.uniform(0.5, 1.5, d)
+    tw, tnw = (torch.tensor(a, dtype=torch.float32, device=cuda) for a in (w, nw))
+    ring = torch.full((3, max(taps - 1, 1), d), -55.0, dtype=torch.float32, device=cuda)
+    hist = {0: rng.standard_normal((n, d)) * 2, 2: rng.standard_normal((n, d))}
+    want = {s: orc.conv_mix(orc.group_rms_norm(x, nw, groups, 1e-5), w) for s, x in hist.items()}
+    at = {0: 0, 2: 0}
+    for step in [[(0, 2)], [(2, 1), (0, 1)], [(0, 1), (2, 2)], [(2, 3), (0, 7)], [(0, 8), (2, 13)]]:
+        rows, slots, poss = [], [], []
+        for s, cnt in step:
+            rows.append(hist[s][at[s]:at[s] + cnt])
+            slots += [s] * cnt
+            poss += list(range(at[s], at[s] + cnt))
+        x = torch.tensor(np.concatenate(rows), dtype=torch.float32, device=cuda)
+        ts = torch.tensor(slots, dtype=torch.int32, device=cuda)
+        tp = torch.tensor(poss, dtype=torch.int32, device=cuda)
+        h, u = ops.group_norm_conv(x, tnw, tw, ts, tp, ring if taps > 1 else None, groups, 1e-5)
+        u = u.cpu().numpy()
+        i = 0
+        for s, cnt in step:
+            assert np.allclose(u[i:i + cnt], want[s][at[s]:at[s] + cnt], rtol=2e-5, atol=2e-5), (taps, groups, step, s)
+            i += cnt
+            at[s] += cnt
+        ops.group_rmsnorm_residual(torch.ones_like(x), torch.ones(d, device=cuda), torch.zeros_like(x), 1, 1e-5, conv_in=h,
+                                   slot=ts, pos=tp, ring=ring if taps > 1 else None, taps=taps)
+    assert at == {0: n, 2: n}
+
+
 def _absorbed_attention(qa, c, pos, sink, scale):
     out = np.zeros_like(qa)
     for t in range(qa.shape[0]):

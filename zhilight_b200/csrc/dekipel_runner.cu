@@ -295,9 +295,10 @@ int alloc_runtime(zl_dekipel* m) {
 int linear(zl_dekipel* m, const void* x, int K, const void* w, int N, void* y, int M, int out_dtype, int epi) {
     const auto& c = m->cfg;
     static const bool no_skinny = getenv("ZL_DEKIPEL_NO_SKINNY") != nullptr;
-    if (!no_skinny && c.dtype != ZL_F32 && epi == ZL_GEMM_EPI_NONE && M <= 32 && K % 32 == 0 && N >= 64 &&
+    if (!no_skinny && c.dtype != ZL_F32 && epi != ZL_GEMM_EPI_SIGMOID_GATE && M <= 32 && K % 32 == 0 && N >= 64 &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0)
-        return zl_dense_gemm_skinny(x, K, w, nullptr, y, M, N, K, c.dtype, out_dtype, c.use_pdl, m->stream);
+        return zl_dense_gemm_skinny_act(x, K, w, nullptr, y, M, N, K, c.dtype, out_dtype, epi == ZL_GEMM_EPI_RELU2 ? 1 : 0,
+                                        c.use_pdl, m->stream);
     return zl_gemm_nt(x, K, 0, w, K, 0, y, N, 0, M, N, K, 1, c.dtype, out_dtype, epi, nullptr, 0, 0, c.use_pdl, m->stream);
 }
 
@@ -305,6 +306,8 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
     const auto& c = m->cfg;
     const int D = c.width, dt = c.dtype, pdl = c.use_pdl, G = c.norm_groups, taps = c.canon_taps;
     cudaStream_t st = m->stream;
+    // ZL_DEKIPEL_UNFUSED=1: one kernel per operator (pre-norm and convolution apart), for A/B and bring-up
+    static const bool fuse = getenv("ZL_DEKIPEL_UNFUSED") == nullptr;
     if (dt == ZL_F32)
         ZL_CHECK_CUDA(launch(k_embed_f32<float>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
                              (const float*)m->embed, m->x, D, c.vocab));
@@ -316,9 +319,14 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
         const auto& lc = L.c;
         const int H = lc.heads, R = lc.kv_rank, own = lc.kv_from < 0;
         // mixer sublayer
-        RCHECK(zl_group_rmsnorm(m->x, D, L.norm1, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl, st));
-        RCHECK(zl_causal_conv_mix(m->hbuf, D, L.canon1, m->d_slots, m->d_pos, (const float*)L.ring1.buf, m->ubuf, D, T, D, taps,
-                                  dt, pdl, st));
+        if (fuse) {
+            RCHECK(zl_group_norm_conv(m->x, D, L.norm1, L.canon1, m->d_slots, m->d_pos, (const float*)L.ring1.buf, m->hbuf, m->ubuf,
+                                      T, D, G, taps, c.eps, dt, pdl, st));
+        } else {
+            RCHECK(zl_group_rmsnorm(m->x, D, L.norm1, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl, st));
+            RCHECK(zl_causal_conv_mix(m->hbuf, D, L.canon1, m->d_slots, m->d_pos, (const float*)L.ring1.buf, m->ubuf, D, T, D,
+                                      taps, dt, pdl, st));
+        }
         RCHECK(linear(m, m->ubuf, D, L.w_in, L.n_in, m->proj, T, ZL_F32, ZL_GEMM_EPI_NONE));
         RCHECK(zl_latent_norm_append(m->proj, L.n_in, 0, lc.q_rank, L.dq_norm, m->cq, L.c_off, R, own ? L.dkv_norm : nullptr,
                                      L.lat_addrs, m->d_slots, m->d_pos, T, c.eps, dt, pdl, st));
@@ -334,11 +342,15 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
         RCHECK(zl_group_rmsnorm_residual(m->y, D, L.norm1b, m->x, D, T, D, G, c.eps, m->hbuf, D, m->d_slots, m->d_pos,
                                          (float*)L.ring1.buf, taps, pdl, st));
         if (lc.ff > 0) {
-            RCHECK(zl_group_rmsnorm(m->x, D, L.norm2, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl, st));
-            RCHECK(zl_causal_conv_mix(m->hbuf, D, L.canon2, m->d_slots, m->d_pos, (const float*)L.ring2.buf, m->ubuf, D, T, D,
-                                      taps, dt, pdl, st));
-            RCHECK(zl_gemm_nt(m->ubuf, D, 0, L.up, D, 0, m->act, lc.ff, 0, T, lc.ff, D, 1, dt, dt, ZL_GEMM_EPI_RELU2, nullptr, 0, 0,
-                              pdl, st));
+            if (fuse) {
+                RCHECK(zl_group_norm_conv(m->x, D, L.norm2, L.canon2, m->d_slots, m->d_pos, (const float*)L.ring2.buf, m->hbuf,
+                                          m->ubuf, T, D, G, taps, c.eps, dt, pdl, st));
+            } else {
+                RCHECK(zl_group_rmsnorm(m->x, D, L.norm2, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl, st));
+                RCHECK(zl_causal_conv_mix(m->hbuf, D, L.canon2, m->d_slots, m->d_pos, (const float*)L.ring2.buf, m->ubuf, D, T, D,
+                                          taps, dt, pdl, st));
+            }
+            RCHECK(linear(m, m->ubuf, D, L.up, lc.ff, m->act, T, dt, ZL_GEMM_EPI_RELU2));
             RCHECK(linear(m, m->act, lc.ff, L.down, D, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
             RCHECK(zl_group_rmsnorm_residual(m->y, D, L.norm2b, m->x, D, T, D, G, c.eps, m->hbuf, D, m->d_slots, m->d_pos,
                                              (float*)L.ring2.buf, taps, pdl, st));

@@ -97,6 +97,56 @@ __global__ void k_causal_conv_mix(const float* __restrict__ h, long long ldh, co
     u[(size_t)t * ldu + c] = from_f32<TO>(cur + acc);
 }
 
+
+// The pre-norm and the convolution in one pass: h[t] = gnorm(x[t]) * w, u[t] = h[t] + conv.  The norm is per row, so the
+// earlier rows the convolution needs are normalised again here when they are rows of this step (the same arithmetic as
+// in their own CTA, hence the same values); otherwise they come from the slot's ring.  grid (T), dynamic shared memory:
+// taps * groups inverse RMS values.
+template <typename TO>
+__global__ void k_group_norm_conv(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
+                                  const float* __restrict__ wt, const int32_t* __restrict__ slot,
+                                  const int32_t* __restrict__ pos, const float* __restrict__ ring, float* __restrict__ h,
+                                  TO* __restrict__ u, int D, int groups, int taps, float eps) {
+    extern __shared__ float inv[];   // [taps][groups]; entry < 0: that row is not in this step
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, s = slot[t], p = pos[t], keep = taps - 1, gs = D / groups;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int pair = warp; pair < taps * groups; pair += nw) {
+        const int back = pair / groups, g = pair - back * groups;
+        const bool here = back == 0 || (t - back >= 0 && slot[t - back] == s && pos[t - back] == p - back);
+        float r = -1.f;
+        if (here) {
+            const float* xr = x + (size_t)(t - back) * ldx + g * gs;
+            float ss = 0.f;
+            for (int i = lane; i < gs; i += 32) {
+                const float v = xr[i];
+                ss = fmaf(v, v, ss);
+            }
+            r = 1.0f / sqrtf(warp_sum(ss) / (float)gs + eps);
+        }
+        if (lane == 0) inv[pair] = r;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const int g = c / gs;
+        const float wc = w[c];
+        const float cur = x[(size_t)t * ldx + c] * inv[g] * wc;
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = keep - j, q = p - back;
+            float v;
+            if (back == 0) v = cur;
+            else if (q < 0) v = 0.f;
+            else if (inv[back * groups + g] >= 0.f) v = x[(size_t)(t - back) * ldx + c] * inv[back * groups + g] * wc;
+            else v = ring[((size_t)s * keep + (q % keep)) * D + c];
+            acc = fmaf(wt[(size_t)c * taps + j], v, acc);
+        }
+        h[(size_t)t * D + c] = cur;
+        u[(size_t)t * D + c] = from_f32<TO>(cur + acc);
+    }
+}
+
 // grid (2, T): part 0 = query latent -> cq[t]; part 1 = key-value latent -> cache row (slot[t], pos[t])
 template <typename TO>
 __global__ void k_latent_norm_append(const float* __restrict__ proj, long long ldp, int q_off, int q_rank,
@@ -179,6 +229,29 @@ extern "C" int zl_causal_conv_mix(const float* h, long long ldh, const float* ta
     else
         e = launch(k_causal_conv_mix<__half>, grid, block, 0, stream, pdl != 0, h, ldh, taps_weight, slot, pos, ring,
                    static_cast<__half*>(u), ldu, D, taps);
+    ZL_CHECK_CUDA(e);
+    return ZL_OK;
+}
+
+extern "C" int zl_group_norm_conv(const float* x, long long ldx, const float* norm_weight, const float* taps_weight,
+                                  const int32_t* slot, const int32_t* pos, const float* ring, float* h, void* u, int T, int D,
+                                  int groups, int taps, float eps, int out_dtype, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(x && norm_weight && taps_weight && slot && pos && h && u && T > 0 && D > 0 && taps >= 1);
+    ZL_CHECK_ARG(groups > 0 && D % groups == 0 && (taps == 1 || ring));
+    ZL_CHECK_ARG(out_dtype == ZL_F16 || out_dtype == ZL_BF16 || out_dtype == ZL_F32);
+    const size_t smem = sizeof(float) * (size_t)taps * groups;
+    ZL_CHECK_SUPPORTED(smem <= 40 * 1024);
+    const dim3 grid(T), block(D >= 2048 ? 256 : 128);
+    cudaError_t e;
+    if (out_dtype == ZL_F32)
+        e = launch(k_group_norm_conv<float>, grid, block, smem, stream, pdl != 0, x, ldx, norm_weight, taps_weight, slot, pos,
+                   ring, h, static_cast<float*>(u), D, groups, taps, eps);
+    else if (out_dtype == ZL_BF16)
+        e = launch(k_group_norm_conv<__nv_bfloat16>, grid, block, smem, stream, pdl != 0, x, ldx, norm_weight, taps_weight, slot,
+                   pos, ring, h, static_cast<__nv_bfloat16*>(u), D, groups, taps, eps);
+    else
+        e = launch(k_group_norm_conv<__half>, grid, block, smem, stream, pdl != 0, x, ldx, norm_weight, taps_weight, slot, pos,
+                   ring, h, static_cast<__half*>(u), D, groups, taps, eps);
     ZL_CHECK_CUDA(e);
     return ZL_OK;
 }

@@ -465,3 +465,13 @@ def latent_attention(q_absorbed, cache, table, slot, pos, sink, scale, splits=1)
     _lib.call("zl_latent_attention", _p(q_absorbed), _p(table), _p(slot), _p(pos), _p(sink), scale, _p(out), t, h, r, splits,
               _p(ws), nbytes, _dt(cache), 0, _stream())
     return out
+
+
+def group_norm_conv(x, norm_weight, taps_weight, slot, pos, ring, groups, eps, out_dtype=torch.float32):
+    """Fused pre-norm + causal convolution: returns (h = group_rmsnorm(x), u = h + conv(h))."""
+    t, d = x.shape
+    h = torch.empty((t, d), dtype=torch.float32, device=x.device)
+    u = torch.empty((t, d), dtype=out_dtype, device=x.device)
+    _lib.call("zl_group_norm_conv", _p(x), d, _p(norm_weight), _p(taps_weight), _p(slot), _p(pos), _p(ring), _p(h), _p(u), t, d,
+              groups, taps_weight.shape[1], eps, _dt(u), 0, _stream())
+    return h, u
