@@ -56,7 +56,8 @@ def tokens_for(cfg, n, seed):
 
 
 # ---------------------------------------------------------------------------------------------- mechanisms alone
-@pytest.mark.parametrize("shape", [(5, 7, 13, 1), (70, 130, 80, 1), (33, 24, 8, 5), (64, 64, 32, 2), (1, 200, 96, 1)])
+@pytest.mark.parametrize("shape", [(5, 7, 13, 1), (70, 130, 80, 1), (33, 24, 8, 5), (64, 64, 32, 2), (1, 200, 96, 1), (8, 70, 64, 3),
+                                   (32, 33, 128, 2), (17, 40, 24, 1), (3, 9, 512, 4)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_gemm_nt_any_shape(cuda, lib, shape, dtype):
     import torch

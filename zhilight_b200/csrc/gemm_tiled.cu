@@ -134,6 +134,74 @@ __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w)
             }
 }
 
+
+// ---- decode-sized M, 16-bit inputs -----------------------------------------------------------------------------------
+// y[b](M <= 8, N) for many small per-head weight blocks: one warp per output column n streams w[b][n][:] once with
+// 16-byte loads and multiplies it with all M rows of x[b], which the CTA holds in shared memory.  fp32 accumulation,
+// warp-shuffle reduction.  grid (ceil(N / 32), batch), 8 warps, 4 columns per warp.
+constexpr int kSmCols = 32;
+
+template <typename T, typename TO, int EPI, int MT>
+__global__ void __launch_bounds__(256) k_gemm_small_m(GemmP p) {
+    extern __shared__ __align__(16) unsigned char sx_raw[];
+    T* sx = reinterpret_cast<T*>(sx_raw);   // [M][K]
+    pdl_trigger();
+    const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* w = static_cast<const T*>(p.w) + (size_t)b * p.wb;
+    const T* x = static_cast<const T*>(p.x) + (size_t)b * p.xb;
+    const int K = p.K, K8 = K / 8;
+    pdl_wait();
+    for (int i = threadIdx.x; i < p.M * K8; i += blockDim.x) {
+        const int m = i / K8, k8 = i - m * K8;
+        *reinterpret_cast<uint4*>(sx + (size_t)m * K + k8 * 8) = *reinterpret_cast<const uint4*>(x + (size_t)m * p.ldx + k8 * 8);
+    }
+    __syncthreads();
+    for (int n = blockIdx.x * kSmCols + warp; n < min(p.N, (int)(blockIdx.x + 1) * kSmCols); n += 8) {
+        float acc[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+        const T* wr = w + (size_t)n * p.ldw;
+        for (int k8 = lane; k8 < K8; k8 += 32) {
+            float wf[8];
+            unpack8<T>(ld_nc_na_u4(wr + k8 * 8), wf);
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m < p.M) {
+                    float xf[8];
+                    unpack8<T>(*reinterpret_cast<const uint4*>(sx + (size_t)m * K + k8 * 8), xf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+                }
+            }
+        }
+        float mine = 0.f;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float v = warp_sum(acc[m]);
+            if (lane == m) mine = v;
+        }
+        if (lane < p.M) {
+            TO* y = static_cast<TO*>(p.y) + (size_t)b * p.yb;
+            y[(size_t)lane * p.ldy + n] = from_f32<TO>(gemm_epilogue<EPI>(mine, p, b, lane, n));
+        }
+    }
+}
+
+template <typename T, typename TO, int EPI>
+static cudaError_t launch_small_m_mt(const GemmP& p, int batch, bool pdl, cudaStream_t st) {
+    const dim3 grid(cdiv(p.N, kSmCols), batch), block(256);
+    const size_t smem = (size_t)p.M * p.K * sizeof(T);
+    if (p.M <= 2) return launch(k_gemm_small_m<T, TO, EPI, 2>, grid, block, smem, st, pdl, p);
+    if (p.M <= 4) return launch(k_gemm_small_m<T, TO, EPI, 4>, grid, block, smem, st, pdl, p);
+    return launch(k_gemm_small_m<T, TO, EPI, 8>, grid, block, smem, st, pdl, p);
+}
+template <typename T, typename TO>
+static cudaError_t launch_small_m(const GemmP& p, int batch, int epi, bool pdl, cudaStream_t st) {
+    if (epi == ZL_GEMM_EPI_RELU2) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_RELU2>(p, batch, pdl, st);
+    if (epi == ZL_GEMM_EPI_SIGMOID_GATE) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_SIGMOID_GATE>(p, batch, pdl, st);
+    return launch_small_m_mt<T, TO, ZL_GEMM_EPI_NONE>(p, batch, pdl, st);
+}
+
 // ---- fp32 inputs ---------------------------------------------------------------------------------------------------
 constexpr int kFK = 16;
 
@@ -229,7 +297,7 @@ extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride
     ZL_CHECK_ARG(out_dtype == in_dtype || out_dtype == ZL_F32);
     ZL_CHECK_ARG(epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_RELU2 || epilogue == ZL_GEMM_EPI_SIGMOID_GATE);
     ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_SIGMOID_GATE || (gate && ldg >= N));
-    ZL_CHECK_ARG(cdiv(M, kGB) <= 65535);
+    ZL_CHECK_ARG(cdiv(M, kGB) <= 65535 && cdiv(N, kSmCols) <= 2147483647);
     GemmP p{x, w, y, gate, ldx, x_batch_stride, ldw, w_batch_stride, ldy, y_batch_stride, ldg, gate_batch_stride, M, N, K};
     const int elem = in_dtype == ZL_F32 ? 4 : 2;
     const bool vx = aligned_for(x, ldx, x_batch_stride, K, elem, batch), vw = aligned_for(w, ldw, w_batch_stride, K, elem, batch);
@@ -242,6 +310,13 @@ extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride
             e = launch(k_gemm_f32<ZL_GEMM_EPI_SIGMOID_GATE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
         else
             e = launch(k_gemm_f32<ZL_GEMM_EPI_NONE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+    } else if (M <= 8 && vx && vw && (size_t)M * K * 2 <= 48 * 1024) {   // few rows: stream the weights once per column
+        if (in_dtype == ZL_BF16)
+            e = out_dtype == ZL_F32 ? launch_small_m<__nv_bfloat16, float>(p, batch, epilogue, pdl != 0, stream)
+                                    : launch_small_m<__nv_bfloat16, __nv_bfloat16>(p, batch, epilogue, pdl != 0, stream);
+        else
+            e = out_dtype == ZL_F32 ? launch_small_m<__half, float>(p, batch, epilogue, pdl != 0, stream)
+                                    : launch_small_m<__half, __half>(p, batch, epilogue, pdl != 0, stream);
     } else if (in_dtype == ZL_BF16) {
         e = out_dtype == ZL_F32 ? launch_mma<__nv_bfloat16, float>(p, batch, epilogue, vx, vw, pdl != 0, stream)
                                 : launch_mma<__nv_bfloat16, __nv_bfloat16>(p, batch, epilogue, vx, vw, pdl != 0, stream);

@@ -41,33 +41,42 @@ __global__ void k_group_rmsnorm(const float* __restrict__ x, long long ldx, cons
     for (int i = threadIdx.x; i < gs; i += blockDim.x) yr[i] = from_f32<TO>(xr[i] * r * w[c0 + i]);
 }
 
+// 1 / sqrt(mean(row[g*gs .. +gs)^2) + eps), computed by the whole CTA (the same order of sums in every CTA)
+__device__ __forceinline__ float group_inv_rms(const float* __restrict__ row, int g, int gs, float eps, float* red) {
+    const float* xr = row + (size_t)g * gs;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    return 1.0f / sqrtf(block_sum(ss, red) / (float)gs + eps);
+}
+
 // x[t] += gnorm(y[t]) * w; optionally h[t] -> ring[slot][pos % (taps-1)] for the rows that are among the last taps-1 of
 // their sequence in this step (rows of one sequence are consecutive, so row t + taps-1 tells).
+// grid (ceil(D / blockDim), T): a CTA owns blockDim channels and computes the sums of the groups they lie in itself.
 __global__ void k_group_rmsnorm_residual(const float* __restrict__ y, long long ldy, const float* __restrict__ w,
                                          float* __restrict__ x, long long ldx, int gs, float eps,
                                          const float* __restrict__ h, long long ldh, const int32_t* __restrict__ slot,
                                          const int32_t* __restrict__ pos, float* __restrict__ ring, int keep, int T, int D) {
     __shared__ float red[32];
+    extern __shared__ float inv[];   // one per group that meets this CTA's channels
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.y, c0 = blockIdx.x * gs;
-    const float* yr = y + (size_t)t * ldy + c0;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-        const float v = yr[i];
-        ss = fmaf(v, v, ss);
+    const int t = blockIdx.y, c0 = blockIdx.x * blockDim.x, c = c0 + threadIdx.x;
+    const int g_lo = c0 / gs, g_hi = min(D - 1, c0 + (int)blockDim.x - 1) / gs;
+    const float* yr = y + (size_t)t * ldy;
+    for (int g = g_lo; g <= g_hi; ++g) {
+        const float r = group_inv_rms(yr, g, gs, eps, red);
+        if (threadIdx.x == 0) inv[g - g_lo] = r;
     }
-    const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)gs + eps);
-    float* xr = x + (size_t)t * ldx + c0;
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) xr[i] = xr[i] + yr[i] * r * w[c0 + i];
+    __syncthreads();
+    if (c >= D) return;
+    x[(size_t)t * ldx + c] += yr[c] * inv[c / gs - g_lo] * w[c];
     if (ring && keep > 0) {
         const int s = slot[t];
         const bool later = t + keep < T && slot[t + keep] == s;   // a row of this sequence keep steps on overwrites it
-        if (!later) {
-            float* dst = ring + ((size_t)s * keep + (pos[t] % keep)) * D + c0;
-            const float* hr = h + (size_t)t * ldh + c0;
-            for (int i = threadIdx.x; i < gs; i += blockDim.x) dst[i] = hr[i];
-        }
+        if (!later) ring[((size_t)s * keep + (pos[t] % keep)) * D + c] = h[(size_t)t * ldh + c];
     }
 }
 
@@ -100,51 +109,44 @@ __global__ void k_causal_conv_mix(const float* __restrict__ h, long long ldh, co
 
 // The pre-norm and the convolution in one pass: h[t] = gnorm(x[t]) * w, u[t] = h[t] + conv.  The norm is per row, so the
 // earlier rows the convolution needs are normalised again here when they are rows of this step (the same arithmetic as
-// in their own CTA, hence the same values); otherwise they come from the slot's ring.  grid (T), dynamic shared memory:
-// taps * groups inverse RMS values.
+// in their own CTA, hence the same values); otherwise they come from the slot's ring.
+// grid (ceil(D / blockDim), T); dynamic shared memory: taps * (groups that meet the CTA's channels) inverse RMS values.
 template <typename TO>
 __global__ void k_group_norm_conv(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
                                   const float* __restrict__ wt, const int32_t* __restrict__ slot,
                                   const int32_t* __restrict__ pos, const float* __restrict__ ring, float* __restrict__ h,
-                                  TO* __restrict__ u, int D, int groups, int taps, float eps) {
-    extern __shared__ float inv[];   // [taps][groups]; entry < 0: that row is not in this step
+                                  TO* __restrict__ u, int D, int gs, int taps, float eps) {
+    __shared__ float red[32];
+    extern __shared__ float inv[];   // [taps][ng]; entry < 0: that row is not in this step
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x, s = slot[t], p = pos[t], keep = taps - 1, gs = D / groups;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int pair = warp; pair < taps * groups; pair += nw) {
-        const int back = pair / groups, g = pair - back * groups;
-        const bool here = back == 0 || (t - back >= 0 && slot[t - back] == s && pos[t - back] == p - back);
-        float r = -1.f;
-        if (here) {
-            const float* xr = x + (size_t)(t - back) * ldx + g * gs;
-            float ss = 0.f;
-            for (int i = lane; i < gs; i += 32) {
-                const float v = xr[i];
-                ss = fmaf(v, v, ss);
-            }
-            r = 1.0f / sqrtf(warp_sum(ss) / (float)gs + eps);
+    const int t = blockIdx.y, s = slot[t], p = pos[t], keep = taps - 1;
+    const int c0 = blockIdx.x * blockDim.x, c = c0 + threadIdx.x;
+    const int g_lo = c0 / gs, g_hi = min(D - 1, c0 + (int)blockDim.x - 1) / gs, ng = g_hi - g_lo + 1;
+    for (int back = 0; back < taps; ++back) {
+        const bool here = back == 0 || (t - back >= 0 && slot[t - back] == s && pos[t - back] == p - back);   // CTA-uniform
+        for (int g = g_lo; g <= g_hi; ++g) {
+            const float r = here ? group_inv_rms(x + (size_t)(t - back) * ldx, g, gs, eps, red) : -1.f;
+            if (threadIdx.x == 0) inv[back * ng + g - g_lo] = r;
         }
-        if (lane == 0) inv[pair] = r;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        const int g = c / gs;
-        const float wc = w[c];
-        const float cur = x[(size_t)t * ldx + c] * inv[g] * wc;
-        float acc = 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int back = keep - j, q = p - back;
-            float v;
-            if (back == 0) v = cur;
-            else if (q < 0) v = 0.f;
-            else if (inv[back * groups + g] >= 0.f) v = x[(size_t)(t - back) * ldx + c] * inv[back * groups + g] * wc;
-            else v = ring[((size_t)s * keep + (q % keep)) * D + c];
-            acc = fmaf(wt[(size_t)c * taps + j], v, acc);
-        }
-        h[(size_t)t * D + c] = cur;
-        u[(size_t)t * D + c] = from_f32<TO>(cur + acc);
+    if (c >= D) return;
+    const int g = c / gs - g_lo;
+    const float wc = w[c];
+    const float cur = x[(size_t)t * ldx + c] * inv[g] * wc;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = keep - j, q = p - back;
+        float v;
+        if (back == 0) v = cur;
+        else if (q < 0) v = 0.f;
+        else if (inv[back * ng + g] >= 0.f) v = x[(size_t)(t - back) * ldx + c] * inv[back * ng + g] * wc;
+        else v = ring[((size_t)s * keep + (q % keep)) * D + c];
+        acc = fmaf(wt[(size_t)c * taps + j], v, acc);
     }
+    h[(size_t)t * D + c] = cur;
+    u[(size_t)t * D + c] = from_f32<TO>(cur + acc);
 }
 
 // grid (2, T): part 0 = query latent -> cq[t]; part 1 = key-value latent -> cache row (slot[t], pos[t])
@@ -171,6 +173,10 @@ __global__ void k_latent_norm_append(const float* __restrict__ proj, long long l
     TO* dst = kv ? static_cast<TO*>(slot_addrs[slot[t]]) + (size_t)pos[t] * kv_rank : cq + (size_t)t * q_rank;
     for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = from_f32<TO>(src[i] * r * w[i]);
 }
+
+// channels per CTA of the row-parallel kernels: a row is spread over several CTAs so that a decode step of one token
+// still fills more than one SM
+static int row_chunk(int D) { return D >= 2048 ? 256 : (D >= 256 ? 128 : 64); }
 
 static int norm_threads(int n) {
     int th = 32;
@@ -206,9 +212,10 @@ extern "C" int zl_group_rmsnorm_residual(const float* y, long long ldy, const fl
                                          zl_stream_t stream) {
     ZL_CHECK_ARG(y && weight && x && T > 0 && D > 0 && groups > 0 && D % groups == 0 && T <= 65535);
     ZL_CHECK_ARG(!ring || (conv_in && slot && pos && taps >= 1));
-    const int gs = D / groups;
-    ZL_CHECK_CUDA(launch(k_group_rmsnorm_residual, dim3(groups, T), dim3(norm_threads(gs)), 0, stream, pdl != 0, y, ldy, weight,
-                         x, ldx, gs, eps, conv_in, ld_conv_in, slot, pos, ring, ring ? taps - 1 : 0, T, D));
+    const int gs = D / groups, th = row_chunk(D);
+    const size_t smem = sizeof(float) * (size_t)((th - 1) / gs + 2);
+    ZL_CHECK_CUDA(launch(k_group_rmsnorm_residual, dim3(cdiv(D, th), T), dim3(th), smem, stream, pdl != 0, y, ldy, weight, x, ldx,
+                         gs, eps, conv_in, ld_conv_in, slot, pos, ring, ring ? taps - 1 : 0, T, D));
     return ZL_OK;
 }
 
@@ -239,19 +246,20 @@ extern "C" int zl_group_norm_conv(const float* x, long long ldx, const float* no
     ZL_CHECK_ARG(x && norm_weight && taps_weight && slot && pos && h && u && T > 0 && D > 0 && taps >= 1);
     ZL_CHECK_ARG(groups > 0 && D % groups == 0 && (taps == 1 || ring));
     ZL_CHECK_ARG(out_dtype == ZL_F16 || out_dtype == ZL_BF16 || out_dtype == ZL_F32);
-    const size_t smem = sizeof(float) * (size_t)taps * groups;
-    ZL_CHECK_SUPPORTED(smem <= 40 * 1024);
-    const dim3 grid(T), block(D >= 2048 ? 256 : 128);
+    const int gs = D / groups, th = row_chunk(D);
+    const size_t smem = sizeof(float) * (size_t)taps * ((th - 1) / gs + 2);
+    ZL_CHECK_SUPPORTED(smem <= 40 * 1024 && T <= 65535);
+    const dim3 grid(cdiv(D, th), T), block(th);
     cudaError_t e;
     if (out_dtype == ZL_F32)
         e = launch(k_group_norm_conv<float>, grid, block, smem, stream, pdl != 0, x, ldx, norm_weight, taps_weight, slot, pos,
-                   ring, h, static_cast<float*>(u), D, groups, taps, eps);
+                   ring, h, static_cast<float*>(u), D, gs, taps, eps);
     else if (out_dtype == ZL_BF16)
         e = launch(k_group_norm_conv<__nv_bfloat16>, grid, block, smem, stream, pdl != 0, x, ldx, norm_weight, taps_weight, slot,
-                   pos, ring, h, static_cast<__nv_bfloat16*>(u), D, groups, taps, eps);
+                   pos, ring, h, static_cast<__nv_bfloat16*>(u), D, gs, taps, eps);
     else
         e = launch(k_group_norm_conv<__half>, grid, block, smem, stream, pdl != 0, x, ldx, norm_weight, taps_weight, slot, pos,
-                   ring, h, static_cast<__half*>(u), D, groups, taps, eps);
+                   ring, h, static_cast<__half*>(u), D, gs, taps, eps);
     ZL_CHECK_CUDA(e);
     return ZL_OK;
 }

@@ -127,27 +127,35 @@ __global__ void __launch_bounds__(kLaThreads) k_latent_attn(LaParams<TC> p) {
     }
 }
 
-// grid (H, T): merge the S partial (max, sum, accumulator) triples of one (token, head) and the sink
+// grid (H, T): merge the S <= 64 partial (max, sum, accumulator) triples of one (token, head) and the sink
 template <typename TC>
 __global__ void k_latent_attn_merge(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                     const float* __restrict__ sink, TC* __restrict__ out, int H, int R, int S) {
+    __shared__ float wgt[64];
     pdl_trigger();
     pdl_wait();
     const size_t th = (size_t)blockIdx.y * H + blockIdx.x;
-    const float* ml = part_ml + th * S * 2;
-    float M = sink[blockIdx.x];
-    for (int s = 0; s < S; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = expf(sink[blockIdx.x] - M);
-    for (int s = 0; s < S; ++s)
-        if (ml[2 * s] != -INFINITY) L += ml[2 * s + 1] * expf(ml[2 * s] - M);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float* ml = part_ml + th * S * 2;
+        const float sk = sink[blockIdx.x];
+        const float m0 = lane < S ? ml[2 * lane] : -INFINITY, m1 = lane + 32 < S ? ml[2 * (lane + 32)] : -INFINITY;
+        const float l0 = lane < S ? ml[2 * lane + 1] : 0.f, l1 = lane + 32 < S ? ml[2 * (lane + 32) + 1] : 0.f;
+        const float M = fmaxf(sk, warp_max(fmaxf(m0, m1)));
+        const float e0 = m0 == -INFINITY ? 0.f : expf(m0 - M), e1 = m1 == -INFINITY ? 0.f : expf(m1 - M);
+        const float L = expf(sk - M) + warp_sum(l0 * e0 + l1 * e1);
+        wgt[lane] = e0 / L;
+        wgt[lane + 32] = e1 / L;
+    }
+    __syncthreads();
+    const float* pa = part_acc + th * S * R;
     for (int r = threadIdx.x; r < R; r += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < S; ++s)
-            if (ml[2 * s] != -INFINITY) a += part_acc[(th * S + s) * R + r] * expf(ml[2 * s] - M);
-        out[th * R + r] = from_f32<TC>(a / L);
+#pragma unroll 4
+        for (int s = 0; s < S; ++s) a = fmaf(pa[(size_t)s * R + r], wgt[s], a);
+        out[th * R + r] = from_f32<TC>(a);
     }
 }
-
 
 // ---- tensor-core variant (bfloat16 caches, kv_rank a multiple of 64 up to 512) -------------------------------------------
 // One CTA = one token x 16 heads x one key range; 4 warps.  The 32-key latent tile is staged once in shared memory
