@@ -382,16 +382,18 @@ def run_compare_dekipel(args):
     rng = np.random.default_rng(0)
     rows = []
     for name, sz in COMPARE_SIZES.items():
-        for kind in ("dekipel", "llama"):
+        for kind in [k for k in ("dekipel", "llama") if k in args.compare_models.split(",")]:
             max_seq = max(ctx, n_prompt) + 4 * (steps + warm) + 64
             if kind == "dekipel":
                 dec = DekipelDecoder.from_config_dict(_dekipel_config(sz), dtype="bf16", max_batch=32, max_seq=max_seq,
-                                                      max_step_tokens=chunk)
+                                                      max_step_tokens=chunk, use_pdl=not args.no_pdl,
+                                                      use_graph=not args.no_graph)
                 cache_row = sz["kv_rank"] * 2 * ((sz["layers"] + 1) // 2)
             else:
                 dec = LlamaDecoder(num_layers=sz["layers"], dim_model=sz["width"], num_heads=sz["heads"], num_kv_heads=8,
                                    dim_head=sz["dim"], dim_ff=sz["ff"], vocab_size=sz["vocab"], quant_type=0, dtype="bf16",
-                                   max_batch=32, max_seq=max_seq, prefill_chunk=chunk)
+                                   max_batch=32, max_seq=max_seq, prefill_chunk=chunk, use_pdl=not args.no_pdl,
+                                   use_graph=not args.no_graph)
                 cache_row = 2 * 8 * sz["dim"] * 2 * sz["layers"]
             dec.init_synthetic(seed=1)
             stream = torch.cuda.ExternalStream(dec.stream())
@@ -454,6 +456,7 @@ def main():
                     help="default: the model's BASELINE quantisation (GPTQ int4 for 8B, bf16 for 1B); int8 / fp8: W8A8 Linear rows")
     ap.add_argument("--prefill-chunk", type=int, default=128, help="tokens per chunked-prefill pass of the TTFT measurement")
     ap.add_argument("--fuse", type=int, default=2, help="0: one kernel per reference op; 1: +RMSNorm fused; 2: +qkv RoPE/KV epilogue")
+    ap.add_argument("--compare-models", default="dekipel,llama", help="--compare-dekipel: which of the two to run")
     ap.add_argument("--compare-dekipel", action="store_true",
                     help="instead of the default workload: Dekipel beside the bf16 Llama decoder at a few layer sizes")
     args = ap.parse_args()

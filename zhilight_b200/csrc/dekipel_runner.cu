@@ -65,6 +65,8 @@ struct zl_dekipel {
 
 namespace {
 
+constexpr int kDefaultPdlMask = 1;
+
 int fail(int line, const std::string& msg, int code = ZL_ERR_STATE) {
     zl_set_last_error(__FILE__, line, msg.c_str());
     return code;
@@ -290,6 +292,22 @@ int alloc_runtime(zl_dekipel* m) {
     return ZL_OK;
 }
 
+// Which kernels of the step are launched with a programmatic dependency (they may start while their predecessor drains
+// and wait inside): 1 skinny Linears, 2 tiled / per-head GEMMs, 4 norm / convolution / residual rows, 8 attention,
+// 16 the tail (gather, final norm, head, pick).  Measured on B200 (1 and 32 rows, two layer sizes): only the skinny
+// Linears of steps with few rows gain (their first weight loads fly before the wait); early-started CTAs of the row
+// kernels and GEMMs take SM slots from the kernel they wait for and cost up to 50 % of a 32-row step.
+// ZL_DEKIPEL_PDL_MASK overrides the default.
+int pdl_mask() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("ZL_DEKIPEL_PDL_MASK");
+        v = e ? atoi(e) : kDefaultPdlMask;
+    }
+    return v;
+}
+int pdl_for(const zl_dekipel* m, int bit) { return (m->cfg.use_pdl && (pdl_mask() & bit)) ? 1 : 0; }
+
 // y (M, N) = x (M, K) @ w (N, K)^T.  Decode-sized 16-bit products whose K suits it stream the weights once through the
 // framework's skinny kernel; everything else goes through the tiled kernel.
 int linear(zl_dekipel* m, const void* x, int K, const void* w, int N, void* y, int M, int out_dtype, int epi) {
@@ -298,13 +316,14 @@ int linear(zl_dekipel* m, const void* x, int K, const void* w, int N, void* y, i
     if (!no_skinny && c.dtype != ZL_F32 && epi != ZL_GEMM_EPI_SIGMOID_GATE && M <= 32 && K % 32 == 0 && N >= 64 &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0)
         return zl_dense_gemm_skinny_act(x, K, w, nullptr, y, M, N, K, c.dtype, out_dtype, epi == ZL_GEMM_EPI_RELU2 ? 1 : 0,
-                                        c.use_pdl, m->stream);
-    return zl_gemm_nt(x, K, 0, w, K, 0, y, N, 0, M, N, K, 1, c.dtype, out_dtype, epi, nullptr, 0, 0, c.use_pdl, m->stream);
+                                        M <= 8 ? pdl_for(m, 1) : 0, m->stream);
+    return zl_gemm_nt(x, K, 0, w, K, 0, y, N, 0, M, N, K, 1, c.dtype, out_dtype, epi, nullptr, 0, 0, pdl_for(m, 2), m->stream);
 }
 
 int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
     const auto& c = m->cfg;
-    const int D = c.width, dt = c.dtype, pdl = c.use_pdl, G = c.norm_groups, taps = c.canon_taps;
+    const int D = c.width, dt = c.dtype, G = c.norm_groups, taps = c.canon_taps;
+    const int pdl_gemm = pdl_for(m, 2), pdl_row = pdl_for(m, 4), pdl_attn = pdl_for(m, 8), pdl_tail = pdl_for(m, 16);
     cudaStream_t st = m->stream;
     // ZL_DEKIPEL_UNFUSED=1: one kernel per operator (pre-norm and convolution apart), for A/B and bring-up
     static const bool fuse = getenv("ZL_DEKIPEL_UNFUSED") == nullptr;
@@ -321,39 +340,39 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
         // mixer sublayer
         if (fuse) {
             RCHECK(zl_group_norm_conv(m->x, D, L.norm1, L.canon1, m->d_slots, m->d_pos, (const float*)L.ring1.buf, m->hbuf, m->ubuf,
-                                      T, D, G, taps, c.eps, dt, pdl, st));
+                                      T, D, G, taps, c.eps, dt, pdl_row, st));
         } else {
-            RCHECK(zl_group_rmsnorm(m->x, D, L.norm1, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl, st));
+            RCHECK(zl_group_rmsnorm(m->x, D, L.norm1, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl_row, st));
             RCHECK(zl_causal_conv_mix(m->hbuf, D, L.canon1, m->d_slots, m->d_pos, (const float*)L.ring1.buf, m->ubuf, D, T, D,
-                                      taps, dt, pdl, st));
+                                      taps, dt, pdl_row, st));
         }
         RCHECK(linear(m, m->ubuf, D, L.w_in, L.n_in, m->proj, T, ZL_F32, ZL_GEMM_EPI_NONE));
         RCHECK(zl_latent_norm_append(m->proj, L.n_in, 0, lc.q_rank, L.dq_norm, m->cq, L.c_off, R, own ? L.dkv_norm : nullptr,
-                                     L.lat_addrs, m->d_slots, m->d_pos, T, c.eps, dt, pdl, st));
+                                     L.lat_addrs, m->d_slots, m->d_pos, T, c.eps, dt, pdl_row, st));
         RCHECK(linear(m, m->cq, lc.q_rank, L.uq, H * lc.dim, m->q, T, dt, ZL_GEMM_EPI_NONE));
         RCHECK(zl_gemm_nt(m->q, (long long)H * lc.dim, lc.dim, L.uk_t, lc.dim, (long long)R * lc.dim, m->qa, (long long)H * R, R,
-                          T, R, lc.dim, H, dt, ZL_F32, ZL_GEMM_EPI_NONE, nullptr, 0, 0, pdl, st));
+                          T, R, lc.dim, H, dt, ZL_F32, ZL_GEMM_EPI_NONE, nullptr, 0, 0, pdl_gemm, st));
         const int splits = zl_latent_attention_splits(T, H, R, max_len);
         RCHECK(zl_latent_attention(m->qa, L.lat_addrs, m->d_slots, m->d_pos, L.sink, lc.scale, m->olat, T, H, R, splits,
-                                   m->attn_ws, m->attn_ws_bytes, dt, pdl, st));
+                                   m->attn_ws, m->attn_ws_bytes, dt, pdl_attn, st));
         RCHECK(zl_gemm_nt(m->olat, (long long)H * R, R, L.uv, R, (long long)lc.vdim * R, m->og, (long long)H * lc.vdim, lc.vdim, T,
-                          lc.vdim, R, H, dt, dt, ZL_GEMM_EPI_SIGMOID_GATE, m->proj + L.g_off, L.n_in, lc.vdim, pdl, st));
+                          lc.vdim, R, H, dt, dt, ZL_GEMM_EPI_SIGMOID_GATE, m->proj + L.g_off, L.n_in, lc.vdim, pdl_gemm, st));
         RCHECK(linear(m, m->og, H * lc.vdim, L.o, D, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
         RCHECK(zl_group_rmsnorm_residual(m->y, D, L.norm1b, m->x, D, T, D, G, c.eps, m->hbuf, D, m->d_slots, m->d_pos,
-                                         (float*)L.ring1.buf, taps, pdl, st));
+                                         (float*)L.ring1.buf, taps, pdl_row, st));
         if (lc.ff > 0) {
             if (fuse) {
                 RCHECK(zl_group_norm_conv(m->x, D, L.norm2, L.canon2, m->d_slots, m->d_pos, (const float*)L.ring2.buf, m->hbuf,
-                                          m->ubuf, T, D, G, taps, c.eps, dt, pdl, st));
+                                          m->ubuf, T, D, G, taps, c.eps, dt, pdl_row, st));
             } else {
-                RCHECK(zl_group_rmsnorm(m->x, D, L.norm2, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl, st));
+                RCHECK(zl_group_rmsnorm(m->x, D, L.norm2, m->hbuf, D, T, D, G, c.eps, ZL_F32, pdl_row, st));
                 RCHECK(zl_causal_conv_mix(m->hbuf, D, L.canon2, m->d_slots, m->d_pos, (const float*)L.ring2.buf, m->ubuf, D, T, D,
-                                          taps, dt, pdl, st));
+                                          taps, dt, pdl_row, st));
             }
             RCHECK(linear(m, m->ubuf, D, L.up, lc.ff, m->act, T, dt, ZL_GEMM_EPI_RELU2));
             RCHECK(linear(m, m->act, lc.ff, L.down, D, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
             RCHECK(zl_group_rmsnorm_residual(m->y, D, L.norm2b, m->x, D, T, D, G, c.eps, m->hbuf, D, m->d_slots, m->d_pos,
-                                             (float*)L.ring2.buf, taps, pdl, st));
+                                             (float*)L.ring2.buf, taps, pdl_row, st));
         }
         if (m->capture && m->layer_dump)
             ZL_CHECK_CUDA(cudaMemcpyAsync(m->layer_dump + (size_t)l * m->tcap * D, m->x, (size_t)T * D * 4,
@@ -362,9 +381,9 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
     if (n_want > 0) {
         ZL_CHECK_CUDA(launch(k_gather_rows_f32, dim3(n_want), dim3(128), 0, st, false, (const float*)m->x,
                              (const int32_t*)m->d_want, m->xw, D));
-        RCHECK(zl_group_rmsnorm(m->xw, D, m->final_norm, m->xn, D, n_want, D, G, c.eps, dt, pdl, st));
+        RCHECK(zl_group_rmsnorm(m->xw, D, m->final_norm, m->xn, D, n_want, D, G, c.eps, dt, pdl_tail, st));
         RCHECK(linear(m, m->xn, D, m->head, c.vocab, m->logits, n_want, ZL_F32, ZL_GEMM_EPI_NONE));
-        RCHECK(zl_argmax(m->logits, m->d_next, n_want, c.vocab, m->argmax_ws, zl_argmax_workspace_bytes(n_want), pdl, st));
+        RCHECK(zl_argmax(m->logits, m->d_next, n_want, c.vocab, m->argmax_ws, zl_argmax_workspace_bytes(n_want), pdl_tail, st));
     }
     return ZL_OK;
 }

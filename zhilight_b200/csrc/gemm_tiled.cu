@@ -4,7 +4,7 @@
 // The decode-sized dense Linear of the framework (dense_gemm.cu) wants K % 32 == 0 and M <= 32 per pass and re-streams
 // the weights for every 32 rows; models whose projection ranks are not multiples of 32, prompt-sized M, and per-head
 // weight blocks go through this kernel instead.  16-bit inputs: 64 x 64 x 32 tiles, mma.sync.m16n8k16 with fp32
-// accumulation, register-prefetched double buffering.  fp32 inputs: 64 x 64 x 16 tiles of plain FMAs (no TF32), every
+// accumulation, a three-stage cp.async pipeline, fragments through ldmatrix.  fp32 inputs: 64 x 64 x 16 tiles of plain FMAs (no TF32), every
 // product and sum in IEEE fp32.
 #include "common.cuh"
 
@@ -59,10 +59,37 @@ __device__ __forceinline__ void mma_in<__nv_bfloat16>(float (&d)[4], const uint3
     mma_16816_bf16(d, a, b0, b1, d);
 }
 
+constexpr int kGStages = 3;
+
+__device__ __forceinline__ void g_cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void g_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void g_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void g_ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+
+// one 64 x 32 tile of a row-major (rows, K) matrix into shared memory: 16-byte cp.async pieces when the layout allows,
+// guarded element loads otherwise; rows / k beyond the matrix become zeros
+template <typename T>
+__device__ __forceinline__ void stage_tile(T (*dst)[kGK + kGPad], const T* base, long long ld, int row0, int rows, int k0,
+                                           int K, bool vec, int lr, int lc) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = lr + half * 32, row = row0 + r, k = k0 + lc;
+        if (vec && row < rows && k < K) g_cp_async16(&dst[r][lc], base + (size_t)row * ld + k);
+        else *reinterpret_cast<uint4*>(&dst[r][lc]) = load8(base, ld, row, rows, k, K, false);
+    }
+}
+
 template <typename T, typename TO, int EPI>
 __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w) {
-    __shared__ __align__(16) T sA[2][kGB][kGK + kGPad];
-    __shared__ __align__(16) T sB[2][kGB][kGK + kGPad];
+    __shared__ __align__(16) T sA[kGStages][kGB][kGK + kGPad];
+    __shared__ __align__(16) T sB[kGStages][kGB][kGK + kGPad];
     pdl_trigger();
     const int b = blockIdx.z;
     const T* x = static_cast<const T*>(p.x) + (size_t)b * p.xb;
@@ -79,45 +106,37 @@ __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
 
-    uint4 rw[2], rx[2];
-    rw[0] = load8(w, p.ldw, n0 + lr, p.N, lc, p.K, vec_w);        // weights do not depend on the predecessor kernel
-    rw[1] = load8(w, p.ldw, n0 + lr + 32, p.N, lc, p.K, vec_w);
-    pdl_wait();
-    rx[0] = load8(x, p.ldx, m0 + lr, p.M, lc, p.K, vec_x);
-    rx[1] = load8(x, p.ldx, m0 + lr + 32, p.M, lc, p.K, vec_x);
     const int steps = cdiv(p.K, kGK);
-    for (int s = 0; s < steps; ++s) {
-        const int buf = s & 1;
-        *reinterpret_cast<uint4*>(&sA[buf][lr][lc]) = rx[0];
-        *reinterpret_cast<uint4*>(&sA[buf][lr + 32][lc]) = rx[1];
-        *reinterpret_cast<uint4*>(&sB[buf][lr][lc]) = rw[0];
-        *reinterpret_cast<uint4*>(&sB[buf][lr + 32][lc]) = rw[1];
-        __syncthreads();   // one barrier per step: buffer `buf` is next written two steps later, after the next barrier
-        if (s + 1 < steps) {
-            const int k = (s + 1) * kGK + lc;
-            rx[0] = load8(x, p.ldx, m0 + lr, p.M, k, p.K, vec_x);
-            rx[1] = load8(x, p.ldx, m0 + lr + 32, p.M, k, p.K, vec_x);
-            rw[0] = load8(w, p.ldw, n0 + lr, p.N, k, p.K, vec_w);
-            rw[1] = load8(w, p.ldw, n0 + lr + 32, p.N, k, p.K, vec_w);
+    pdl_wait();
+    for (int s = 0; s < kGStages - 1; ++s) {
+        if (s < steps) {
+            stage_tile<T>(sA[s], x, p.ldx, m0, p.M, s * kGK, p.K, vec_x, lr, lc);
+            stage_tile<T>(sB[s], w, p.ldw, n0, p.N, s * kGK, p.K, vec_w, lr, lc);
         }
+        g_cp_commit();
+    }
+    for (int s = 0; s < steps; ++s) {
+        const int buf = s % kGStages;
+        g_cp_wait<kGStages - 2>();   // tile s has landed (one younger group may still fly)
+        __syncthreads();             // ... for every thread; and every warp is done with tile s - 1, whose buffer is refilled now
+        if (s + kGStages - 1 < steps) {
+            const int nb = (s + kGStages - 1) % kGStages, k0 = (s + kGStages - 1) * kGK;
+            stage_tile<T>(sA[nb], x, p.ldx, m0, p.M, k0, p.K, vec_x, lr, lc);
+            stage_tile<T>(sB[nb], w, p.ldw, n0, p.N, k0, p.K, vec_w, lr, lc);
+        }
+        g_cp_commit();
 #pragma unroll
         for (int kk = 0; kk < kGK; kk += 16) {
-            uint32_t a[2][4];
+            uint32_t a[2][4], bq[2][4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int r = wm + i * 16 + g;
-                a[i][0] = *reinterpret_cast<const uint32_t*>(&sA[buf][r][kk + 2 * t]);
-                a[i][1] = *reinterpret_cast<const uint32_t*>(&sA[buf][r + 8][kk + 2 * t]);
-                a[i][2] = *reinterpret_cast<const uint32_t*>(&sA[buf][r][kk + 2 * t + 8]);
-                a[i][3] = *reinterpret_cast<const uint32_t*>(&sA[buf][r + 8][kk + 2 * t + 8]);
-            }
+            for (int i = 0; i < 2; ++i) g_ldmatrix_x4(a[i], &sA[buf][wm + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj)   // two 8-column tiles per ldmatrix: {b0, b1} of tile 2jj, {b0, b1} of tile 2jj + 1
+                g_ldmatrix_x4(bq[jj], &sB[buf][wn + jj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int c = wn + j * 8 + g;
-                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sB[buf][c][kk + 2 * t]);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sB[buf][c][kk + 2 * t + 8]);
-                mma_in<T>(acc[0][j], a[0], b0, b1);
-                mma_in<T>(acc[1][j], a[1], b0, b1);
+                mma_in<T>(acc[0][j], a[0], bq[j >> 1][(j & 1) * 2], bq[j >> 1][(j & 1) * 2 + 1]);
+                mma_in<T>(acc[1][j], a[1], bq[j >> 1][(j & 1) * 2], bq[j >> 1][(j & 1) * 2 + 1]);
             }
         }
     }

@@ -413,7 +413,7 @@ extern "C" int zl_latent_attention_splits(int T, int heads, int kv_rank, int max
     const int ctas = T * cdiv(heads, lm_eligible(ZL_BF16, kv_rank) ? kLmRows : la_heads_per_cta(heads, kv_rank));
     const int want = 2 * device_sm_count();
     if (ctas >= want || max_len <= 4 * kLaKeys) return 1;
-    int s = cdiv(want, ctas);
+    int s = want / ctas;   // rounded down: one wave of CTAs, no tail
     const int by_len = cdiv(max_len, 4 * kLaKeys);
     if (s > by_len) s = by_len;
     return s < 1 ? 1 : (s > 64 ? 64 : s);
