@@ -174,7 +174,7 @@ def _absorbed_attention(qa, c, pos, sink, scale):
     return out
 
 
-@pytest.mark.parametrize("heads,rank", [(3, 24), (8, 128), (5, 40), (1, 7), (40, 128)])
+@pytest.mark.parametrize("heads,rank", [(3, 24), (8, 128), (5, 40), (1, 7), (40, 128), (6, 192), (4, 320), (17, 512), (2, 64)])
 def test_latent_attention_far_key_sink_and_tile_edges(cuda, lib, heads, rank):
     """One query row is lined up with a key far back and scaled so that this key carries the softmax; another row meets
     a sink that outweighs every key; the positions sit on and around the kernel's 32-key tiles; rows after a token's own

@@ -5,9 +5,9 @@
 // (qa_h = W_uk,h^T q_h, a per-head GEMM before this kernel), so that score_h(i, j) = scale * qa_h(i) . c_j, and the
 // probabilities are applied to the latents themselves (o_h = sum_j p_j c_j); W_uv,h follows as a per-head GEMM.  All
 // heads of a token read the same latent rows: multi-query attention with head size kv_rank whose K and V are one array.
-// The softmax denominator of head h additionally holds exp(sink_h): a term with no key and no value, not scaled.  It
-// enters the running (max, sum) pair as its initial value (max = sink_h, sum = 1), or in the merge when the keys of a
-// token are split over several CTAs.  Scores, probabilities and the accumulation are fp32.
+// The softmax normaliser of head h has one extra term, exp(sink_h), that belongs to no position: it adds to the sum only,
+// unscaled, once per head and query.  It enters the running (max, sum) pair as its initial value (max = sink_h, sum = 1),
+// or in the merge when the keys of a token are split over several CTAs.  Scores, probabilities and the accumulation are fp32.
 //
 // Token t of a step sees the rows 0 .. pos[t] of its slot; the step's own latents are appended before this kernel, so
 // one kernel serves prompt portions (consecutive positions of one slot) and decode batches (one token per slot).
@@ -159,12 +159,13 @@ __global__ void k_latent_attn_merge(const float* __restrict__ part_acc, const fl
 
 // ---- tensor-core variant (bfloat16 caches, kv_rank a multiple of 64 up to 512) -------------------------------------------
 // One CTA = one token x 16 heads x one key range; 4 warps.  The 32-key latent tile is staged once in shared memory
-// (cp.async, double buffered) and serves both products: S = Qa C^T (contraction over kv_rank, split in quarters over the
+// (cp.async, three tiles in flight) and serves both products: S = Qa C^T (contraction over kv_rank, split in quarters over the
 // warps, the partial 16 x 32 score tiles summed through shared memory in a fixed order) and O += P C (each warp owns a
 // quarter of the kv_rank output columns; C is read through ldmatrix.trans).  Scores, softmax and O are fp32; Qa and P
 // enter the MMAs as bfloat16.
 constexpr int kLmKeys = 32;
 constexpr int kLmRows = 16;
+constexpr int kLmStages = 3;   // latent tiles in flight per CTA
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -186,8 +187,8 @@ template <int NK>   // kv_rank = 64 * NK: every warp contracts over 16 * NK and 
 __global__ void __launch_bounds__(128) k_latent_attn_mma(LaParams<__nv_bfloat16> p) {
     constexpr int RQ = 16 * NK, R = 4 * RQ, RP = R + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* sc = reinterpret_cast<__nv_bfloat16*>(smem_raw);                       // [2][32][RP]
-    float* ss = reinterpret_cast<float*>(smem_raw + (size_t)2 * kLmKeys * RP * 2);         // [4][16][34]
+    __nv_bfloat16* sc = reinterpret_cast<__nv_bfloat16*>(smem_raw);                       // [stages][32][RP]
+    float* ss = reinterpret_cast<float*>(smem_raw + (size_t)kLmStages * kLmKeys * RP * 2);   // [4][16][34]
     pdl_trigger();
     pdl_wait();
     const int h0 = blockIdx.x * kLmRows, t = blockIdx.y, split = blockIdx.z;
@@ -238,11 +239,14 @@ __global__ void __launch_bounds__(128) k_latent_attn_mma(LaParams<__nv_bfloat16>
     };
     const int n_tiles = hi > lo ? cdiv(hi - lo, kLmKeys) : 0;
     if (n_tiles > 0) stage(lo, 0);
+    if (n_tiles > 1) stage(lo + kLmKeys, 1);
+    else cp_async_commit();
     for (int it = 0; it < n_tiles; ++it) {
-        const int j0 = lo + it * kLmKeys, buf = it & 1;
-        cp_async_wait<0>();
-        __syncthreads();   // this tile has landed; every warp is done with the previous round (other buffer, score tiles)
-        if (it + 1 < n_tiles) stage(j0 + kLmKeys, buf ^ 1);   // lands while this round computes
+        const int j0 = lo + it * kLmKeys, buf = it % kLmStages;
+        cp_async_wait<1>();   // all but the youngest group: tile `it` has landed
+        __syncthreads();      // ... for every thread; every warp is done with round it - 1 (its buffer, the score tiles)
+        if (it + 2 < n_tiles) stage(j0 + 2 * kLmKeys, (it + 2) % kLmStages);   // two tiles ahead of the math
+        else cp_async_commit();
         const __nv_bfloat16* ct = sc + (size_t)buf * kLmKeys * RP;
         // partial scores over this warp's quarter of kv_rank
         float s[4][4];
@@ -343,17 +347,23 @@ __global__ void __launch_bounds__(128) k_latent_attn_mma(LaParams<__nv_bfloat16>
 
 static bool lm_eligible(int dtype, int R) {
     static const bool off = getenv("ZL_LATENT_ATTN_NO_MMA") != nullptr;
-    return !off && dtype == ZL_BF16 && (R == 64 || R == 128 || R == 256 || R == 512);
+    return !off && dtype == ZL_BF16 && R % 64 == 0 && R >= 64 && R <= 512;
 }
-static size_t lm_smem_bytes(int R) { return (size_t)2 * kLmKeys * (R + 8) * 2 + (size_t)4 * kLmRows * 34 * 4; }
+static size_t lm_smem_bytes(int R) { return (size_t)kLmStages * kLmKeys * (R + 8) * 2 + (size_t)4 * kLmRows * 34 * 4; }
 
 static int lm_launch(const LaParams<__nv_bfloat16>& p, int T, bool pdl, cudaStream_t st) {
     const size_t smem = lm_smem_bytes(p.R);
     const dim3 grid(cdiv(p.H, kLmRows), T, p.S), block(128);
-    if (p.R == 64) ZL_CHECK_CUDA(launch(k_latent_attn_mma<1>, grid, block, smem, st, pdl, p));
-    else if (p.R == 128) ZL_CHECK_CUDA(launch(k_latent_attn_mma<2>, grid, block, smem, st, pdl, p));
-    else if (p.R == 256) ZL_CHECK_CUDA(launch(k_latent_attn_mma<4>, grid, block, smem, st, pdl, p));
-    else ZL_CHECK_CUDA(launch(k_latent_attn_mma<8>, grid, block, smem, st, pdl, p));
+    switch (p.R / 64) {
+        case 1: ZL_CHECK_CUDA(launch(k_latent_attn_mma<1>, grid, block, smem, st, pdl, p)); break;
+        case 2: ZL_CHECK_CUDA(launch(k_latent_attn_mma<2>, grid, block, smem, st, pdl, p)); break;
+        case 3: ZL_CHECK_CUDA(launch(k_latent_attn_mma<3>, grid, block, smem, st, pdl, p)); break;
+        case 4: ZL_CHECK_CUDA(launch(k_latent_attn_mma<4>, grid, block, smem, st, pdl, p)); break;
+        case 5: ZL_CHECK_CUDA(launch(k_latent_attn_mma<5>, grid, block, smem, st, pdl, p)); break;
+        case 6: ZL_CHECK_CUDA(launch(k_latent_attn_mma<6>, grid, block, smem, st, pdl, p)); break;
+        case 7: ZL_CHECK_CUDA(launch(k_latent_attn_mma<7>, grid, block, smem, st, pdl, p)); break;
+        default: ZL_CHECK_CUDA(launch(k_latent_attn_mma<8>, grid, block, smem, st, pdl, p)); break;
+    }
     if (p.S > 1)
         ZL_CHECK_CUDA(launch(k_latent_attn_merge<__nv_bfloat16>, dim3(p.H, T), dim3(128), 0, st, pdl, (const float*)p.part_acc,
                              (const float*)p.part_ml, p.sink, static_cast<__nv_bfloat16*>(p.out), p.H, p.R, p.S));
@@ -428,6 +438,9 @@ extern "C" int zl_latent_attention_prepare(int heads, int kv_rank, int dtype) {
     if (lm_eligible(dtype, kv_rank) && lm_smem_bytes(kv_rank) > 48 * 1024) {
         const int b = (int)lm_smem_bytes(kv_rank);
         ZL_CHECK_CUDA(cudaFuncSetAttribute(k_latent_attn_mma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
+        ZL_CHECK_CUDA(cudaFuncSetAttribute(k_latent_attn_mma<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
+        ZL_CHECK_CUDA(cudaFuncSetAttribute(k_latent_attn_mma<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
+        ZL_CHECK_CUDA(cudaFuncSetAttribute(k_latent_attn_mma<7>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
         ZL_CHECK_CUDA(cudaFuncSetAttribute(k_latent_attn_mma<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     }
     if (smem <= 48 * 1024) return ZL_OK;

@@ -3,7 +3,7 @@
 Dekipel is a decoder-only family of latent-attention layers: low-rank query and key-value latents, no positional
 rotation, a causal softmax with a per-head sink, a sigmoid output gate, optionally another layer's latent cache; every
 sublayer sits between a pre- and a post-norm (RMS norm in groups) and reads its input through a short causal
-convolution; the feed-forward is relu^2.  config.json gives every size and constant:
+convolution; the feed-forward is relu^2.  All sizes and constants are read from config.json:
 
     {"architecture": "Dekipel", "vocab": V, "width": D, "norm": {"eps": e, "groups": G}, "canon": {"taps": K},
      "layers": [{"type": "latent_attention",
@@ -62,7 +62,7 @@ class DekipelConfig:
                 raise ValueError("layer %d: unknown feed-forward kind %r" % (i, mlp.get("kind")))
             kv_from = mx.get("kv_from")
             layers.append(dict(heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx["vdim"]), q_rank=int(mx["q_rank"]),
-                               kv_rank=int(mx["kv_rank"]), scale=float(mx["scale"]),
+                               kv_rank=int(mx["kv_rank"]), scale=float(mx.get("scale", int(mx["dim"]) ** -0.5)),
                                kv_from=-1 if kv_from is None else int(kv_from), ff=0 if mlp is None else int(mlp["ff"])))
         norm, canon = d.get("norm", {}), d.get("canon", {})
         return cls(d["vocab"], d["width"], layers, norm.get("eps", 1e-5), norm.get("groups", 1), canon.get("taps", 1))
@@ -143,10 +143,15 @@ class DekipelDecoder:
 
     def load_state_dict(self, state_dict):
         """name -> numpy array: bfloat16 bit patterns (safetensors_io.Bf16Array) or float32."""
+        needed = self.config.tensor_shapes()
         for name, arr in state_dict.items():
             a = np.ascontiguousarray(arr)
+            if name not in needed:
+                continue                      # a checkpoint may carry tensors this family does not use
             if not (is_bf16(arr) or a.dtype == np.float32):
                 raise ValueError("tensor %s: expected bfloat16 or float32, got %s" % (name, a.dtype))
+            if tuple(a.shape) != tuple(needed[name]):
+                raise ValueError("tensor %s: shape %s, expected %s" % (name, tuple(a.shape), tuple(needed[name])))
             rows, cols = (1, a.size) if a.ndim <= 1 else (a.shape[0], a.size // a.shape[0])
             _lib.check(self.lib.zl_dekipel_load_tensor(self.h, name.encode(), a.ctypes.data_as(ctypes.c_void_p), rows, cols,
                                                        a.itemsize))
