@@ -403,7 +403,14 @@ int zl_llama_bench_gemms(zl_llama_t* m, int B, int iters, float* ms, int* launch
 /* ------------------------------------------------------------------------------------------ *
  * Building blocks of layers with an fp32 residual stream, grouped norms, short convolutions and latent attention
  * ------------------------------------------------------------------------------------------ */
-enum { ZL_GEMM_EPI_NONE = 0, ZL_GEMM_EPI_RELU2 = 1 /* max(v,0)^2 */, ZL_GEMM_EPI_SIGMOID_GATE = 2 /* v * sigmoid(gate) */ };
+enum {
+    ZL_GEMM_EPI_NONE = 0,
+    ZL_GEMM_EPI_RELU2 = 1 /* max(v,0)^2 */,
+    ZL_GEMM_EPI_SIGMOID_GATE = 2 /* v * sigmoid(gate) */,
+    ZL_GEMM_EPI_TANH = 3,
+    ZL_GEMM_EPI_GLU_CLAMP = 4 /* columns 2j, 2j+1 = gate, up -> column j: g = min(gate, limit), u = clamp(up, +-limit),
+                                 g * sigmoid(alpha * g) * (u + beta); grouped call only */
+};
 /* y[b](M,N) = epi(x[b](M,K) @ w[b](N,K)^T), b < batch, element strides per batch entry; any M, N, K.  in_dtype
  * ZL_F16 / ZL_BF16 (tensor cores, fp32 accumulation) or ZL_F32 (plain fp32 FMAs, no reduced-precision mode);
  * out_dtype = in_dtype or ZL_F32; gate (fp32, same indexing as y with ldg / gate_batch_stride) for the gate epilogue. */
@@ -411,6 +418,18 @@ int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride, const voi
                long long w_batch_stride, void* y, long long ldy, long long y_batch_stride, int M, int N, int K, int batch,
                int in_dtype, int out_dtype, int epilogue, const float* gate, long long ldg, long long gate_batch_stride,
                int pdl, zl_stream_t stream);
+/* One problem with a per-column fp32 bias (NULL: none) added before the epilogue (none, relu^2 or tanh). */
+int zl_gemm_nt_bias(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y, long long ldy,
+                    int M, int N, int K, int in_dtype, int out_dtype, int epilogue, int pdl, zl_stream_t stream);
+/* Grouped problems for mixtures of experts.  A list of rows sorted by group: group g owns the list entries
+ * group_offsets[g] .. group_offsets[g+1] (device, groups + 1 ints) and the weight block w + g * w_group_stride (N, K).
+ * List entry i reads row x_rows[i] of x (NULL: row i) and writes row y_rows[i] of y (NULL: row i).  max_rows bounds the
+ * rows of any group (the step's row count); the offsets are read on the device, so the call can be captured in a graph.
+ * Epilogue none, or the clamped gated unit over column pairs (y has N / 2 columns). */
+int zl_gemm_nt_grouped(const void* x, long long ldx, const int32_t* x_rows, const void* w, long long ldw,
+                       long long w_group_stride, void* y, long long ldy, const int32_t* y_rows, const int32_t* group_offsets,
+                       int groups, int max_rows, int N, int K, int in_dtype, int out_dtype, int epilogue, float limit,
+                       float alpha, float beta, int pdl, zl_stream_t stream);
 /* y[t] = w * x[t] / sqrt(mean(x[t]^2 over each of `groups` equal consecutive parts) + eps); x fp32, y out_dtype. */
 int zl_group_rmsnorm(const float* x, long long ldx, const float* weight, void* y, long long ldy, int T, int D, int groups,
                      float eps, int out_dtype, int pdl, zl_stream_t stream);
@@ -490,6 +509,110 @@ zl_stream_t zl_dekipel_stream(zl_dekipel_t* m);
 int zl_dekipel_capture_layers(zl_dekipel_t* m, int on);
 int zl_dekipel_read_layers(zl_dekipel_t* m, float* out_host, int T);
 int zl_dekipel_stats(zl_dekipel_t* m, double* weight_bytes, int* kernels_per_step);
+
+/* ------------------------------------------------------------------------------------------ *
+ * Building blocks of layers with per-head norms, rotated and cached keys, recurrent state and routed experts
+ * ------------------------------------------------------------------------------------------ */
+/* Rotation frequencies f_i = base^(-2i/dims), i < dims/2, with YaRN scaling when factor > 0: with
+ * dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims-1) and
+ * ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i), and
+ * cos / sin are scaled by mscale = 0.1 ln(factor) + 1 (1 without scaling).  Host function; out (dims/2) floats. */
+int zl_rope_inv_freq_yarn(double base, int dims, double factor, double original, double fast, double slow, float* out,
+                          float* mscale);
+/* From a fused projection row proj[t] (fp32) to attention operands: per query head RMS norm over `dim` times q_weight
+ * (dim), rotation of the first rot_dims dimensions in adjacent pairs (2i, 2i+1) by pos[t] * inv_freq[i] (cos, sin times
+ * mscale), -> q_out (T, heads * dim) of `dtype`; when k_off >= 0 the same for the key heads (k_weight) -> row pos[t] of
+ * k_addrs[slot[t]] ((max_seq, kv_heads, dim)), and every value head divided by its RMS over `vdim` -> row pos[t] of
+ * v_addrs[slot[t]] ((max_seq, kv_heads, vdim)). */
+int zl_qkv_headnorm_rope_append(const float* proj, long long ldp, int q_off, int k_off, int v_off, int heads, int kv_heads,
+                                int dim, int vdim, const float* q_weight, const float* k_weight, const float* inv_freq,
+                                int rot_dims, float mscale, float eps, void* q_out, void* const* k_addrs,
+                                void* const* v_addrs, const int32_t* slot, const int32_t* pos, int T, int dtype, int pdl,
+                                zl_stream_t stream);
+/* Causal attention over the slots' caches: query head h uses key/value head h / (heads / kv_heads);
+ * p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i)) with s = scale * q . k (sink NULL: 0, i.e. one added to the
+ * denominator); out (T, heads * vdim) of `dtype`, head h times sigmoid(gate[t * ldg + h]) when gate != NULL.
+ * splits > 1 cuts the keys of every token over that many CTAs (decode with long contexts); workspace of
+ * zl_sink_attention_workspace_bytes. */
+size_t zl_sink_attention_workspace_bytes(int T, int heads, int vdim, int splits);
+int zl_sink_attention_splits(int T, int heads, int kv_heads, int max_len);
+int zl_sink_attention(const void* q, void* const* k_addrs, void* const* v_addrs, const int32_t* slot, const int32_t* pos,
+                      const float* sink, const float* gate, long long ldg, float scale, void* out, int T, int heads,
+                      int kv_heads, int dim, int vdim, int splits, void* workspace, size_t workspace_bytes, int dtype,
+                      int pdl, zl_stream_t stream);
+/* y[t][h] = o[t][h] / sqrt(mean(o[t][h]^2 over vdim) + eps) * weight[h * vdim + c] * sigmoid(gate[t * ldg + h * vdim + c]);
+ * weight and gate may be NULL. */
+int zl_head_rmsnorm_gate(const float* o, long long ldo, const float* weight, const float* gate, long long ldg, void* y,
+                         long long ldy, int T, int heads, int vdim, float eps, int out_dtype, int pdl, zl_stream_t stream);
+/* x[t] += weight * s / sqrt(mean(s^2) + eps), s = sum_p coef[t * n_parts + p] * parts[(t * n_parts + p) * ldp ..] (coef
+ * NULL: ones); x fp32.  x_act != NULL also receives the new x[t] rounded to act_dtype (the next Linear's input). */
+int zl_rmsnorm_residual_combine(const float* parts, long long ldp, const float* coef, int n_parts, const float* weight,
+                                float* x, long long ldx, void* x_act, int act_dtype, int T, int D, float eps, int pdl,
+                                zl_stream_t stream);
+/* Generalized delta rule over the runs of a step (run i = rows run_row0[i] .. + run_len[i], one slot, consecutive
+ * positions): per head a (dim_k, dim_v) fp32 state S in state_addrs[slot] ((heads, dim_k, dim_v)), zero at position 0,
+ * S <- diag(w) S - (a * u)(u^T S) + k v^T, o = S^T r, with u = k / sqrt(sum(k^2) + unit_eps),
+ * w = exp(-decay_scale * sigmoid(decay_logit)), a = sigmoid(rate_logit).  All inputs fp32 (T, heads * dim). */
+int zl_delta_rule_prepare(int dim_k, int dim_v);
+int zl_delta_rule(const float* r, long long ld_r, const float* k, long long ld_k, const float* v, long long ld_v,
+                  const float* rate_logit, long long ld_a, const float* decay_logit, long long ld_w, float decay_scale,
+                  float unit_eps, const int32_t* run_row0, const int32_t* run_len, int runs, const int32_t* slot,
+                  const int32_t* pos, void* const* state_addrs, float* o, long long ld_o, int heads, int dim_k, int dim_v,
+                  int pdl, zl_stream_t stream);
+/* Routing of a mixture of experts: logits W_router x[t] (fp32), scores (sigmoid, or softmax over the experts), the
+ * `top` largest of score + correction (NULL: none), weights = their scores (renormalize: divided by their sum) ->
+ * top_experts / top_weights (T, top); and the (token, choice) pairs sorted by expert for zl_gemm_nt_grouped:
+ * group_offsets (experts + 1), list_token / list_pair (T * top). */
+enum { ZL_MOE_SCORE_SIGMOID = 0, ZL_MOE_SCORE_SOFTMAX = 1 };
+int zl_moe_route(const float* x, long long ldx, const float* w_router, const float* correction, int32_t* top_experts,
+                 float* top_weights, int32_t* group_offsets, int32_t* list_token, int32_t* list_pair, int T, int D,
+                 int experts, int top, int score_fn, int renormalize, int pdl, zl_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ *
+ * Kodupel: decoder-only model whose layers are listed one by one: the mixer is attention (grouped key/value heads,
+ * biased projections, per-head query / key RMS norm, partial rotation in adjacent pairs with YaRN frequencies, value
+ * heads of unit RMS, a softmax with one added to the denominator, one sigmoid gate per head, optionally another
+ * layer's key/value cache) or a generalized delta rule (a recurrent per-head state); the feed-forward is a mixture
+ * of clamped gated experts chosen by sigmoid scores plus a correction; RMS norms with weight 1 + w sit on the
+ * sublayers' outputs only; the residual stream is fp32.  Same driver shape as zl_dekipel_*.
+ * ------------------------------------------------------------------------------------------ */
+enum { ZL_MIXER_ATTENTION = 0, ZL_MIXER_GENERAL_DELTA = 1 };
+typedef struct zl_kodupel zl_kodupel_t;
+typedef struct zl_kodupel_layer {
+    int type;              /* ZL_MIXER_* */
+    int heads, kv_heads, dim, vdim;
+    int kv_from;           /* attention: -1 own keys and values; j: reads layer j's caches */
+    int rot_dims;          /* attention: rotated dimensions of every head (even, <= dim; 0: none) */
+    float rot_base, yarn_factor /* 0: no scaling */, yarn_original, yarn_fast, yarn_slow;
+    float scale;           /* attention: score scale */
+    int decay_rank;        /* delta rule: inner size of the decay's two-matrix path */
+    int experts, top, ff;  /* experts 0: no feed-forward sublayer */
+    float limit;           /* clamp of the experts' gate and up projections */
+} zl_kodupel_layer_t;
+typedef struct zl_kodupel_config {
+    int num_layers, width, vocab;
+    float eps, embed_scale;
+    int dtype; /* ZL_BF16 or ZL_F32 */
+    int max_batch, max_seq, max_step_tokens;
+    int use_pdl, use_graph;
+} zl_kodupel_config_t;
+int zl_kodupel_create(const zl_kodupel_config_t* cfg, const zl_kodupel_layer_t* layers, zl_kodupel_t** out);
+void zl_kodupel_destroy(zl_kodupel_t* m);
+int zl_kodupel_load_tensor(zl_kodupel_t* m, const char* name, const void* data_host, int rows, int cols, int elem_bytes);
+int zl_kodupel_init_synthetic(zl_kodupel_t* m, uint64_t seed);
+int zl_kodupel_finalize(zl_kodupel_t* m);
+/* Same contract as zl_dekipel_step. */
+int zl_kodupel_step(zl_kodupel_t* m, const int32_t* tokens_host, const int32_t* slots_host, const int32_t* positions_host,
+                    int T, const int32_t* want_rows_host, int n_want, float* logits_host, int32_t* next_host);
+int zl_kodupel_set_state(zl_kodupel_t* m, const int32_t* tokens_host, const int32_t* positions_host, int B);
+int zl_kodupel_step_device(zl_kodupel_t* m, int B);
+int zl_kodupel_sync(zl_kodupel_t* m);
+zl_stream_t zl_kodupel_stream(zl_kodupel_t* m);
+int zl_kodupel_capture_layers(zl_kodupel_t* m, int on);
+int zl_kodupel_read_layers(zl_kodupel_t* m, float* out_host, int T);
+int zl_kodupel_stats(zl_kodupel_t* m, double* weight_bytes, int* kernels_per_step);
+/* Copies one slot's recurrent state of layer `layer` ((heads, dim, dim) fp32) to the host (tests). */
+int zl_kodupel_read_state(zl_kodupel_t* m, int layer, int slot, float* out_host);
 
 #ifdef __cplusplus
 }

@@ -88,6 +88,8 @@ def parse_header(path=HEADER):
     src = re.sub(r"typedef struct zl_w4_fused_args \{.*?\} zl_w4_fused_args_t;", " ", src, flags=re.S)
     src = re.sub(r"typedef struct zl_dekipel_layer \{.*?\} zl_dekipel_layer_t;", " ", src, flags=re.S)
     src = re.sub(r"typedef struct zl_dekipel_config \{.*?\} zl_dekipel_config_t;", " ", src, flags=re.S)
+    src = re.sub(r"typedef struct zl_kodupel_layer \{.*?\} zl_kodupel_layer_t;", " ", src, flags=re.S)
+    src = re.sub(r"typedef struct zl_kodupel_config \{.*?\} zl_kodupel_config_t;", " ", src, flags=re.S)
     src = re.sub(r"enum \{.*?\};", " ", src, flags=re.S)
     protos = {}
     for m in re.finditer(r"([A-Za-z_][\w \*]*?)\b(zl_\w+)\s*\(([^;{}]*?)\)\s*;", src):

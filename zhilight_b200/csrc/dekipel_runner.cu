@@ -72,11 +72,6 @@ int fail(int line, const std::string& msg, int code = ZL_ERR_STATE) {
     return code;
 }
 
-template <typename TS, typename TD>
-__global__ void k_convert(const TS* __restrict__ src, TD* __restrict__ dst, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dst[i] = from_f32<TD>(to_f32<TS>(src[i]));
-}
 // src (heads * dim, R) -> dst (heads, R, dim)
 template <typename TS, typename TD>
 __global__ void k_convert_head_transpose(const TS* __restrict__ src, TD* __restrict__ dst, int heads, int dim, int R) {
@@ -85,89 +80,6 @@ __global__ void k_convert_head_transpose(const TS* __restrict__ src, TD* __restr
     const int d = (int)(i % dim), r = (int)((i / dim) % R), h = (int)(i / ((size_t)dim * R));
     dst[i] = from_f32<TD>(to_f32<TS>(src[((size_t)h * dim + d) * R + r]));
 }
-template <typename TW>
-__global__ void k_embed_f32(const int32_t* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out, int D,
-                            int vocab) {
-    pdl_trigger();
-    pdl_wait();
-    int id = ids[blockIdx.x];
-    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
-    for (int i = threadIdx.x; i < D; i += blockDim.x) out[(size_t)blockIdx.x * D + i] = to_f32<TW>(table[(size_t)id * D + i]);
-}
-__global__ void k_gather_rows_f32(const float* __restrict__ src, const int32_t* __restrict__ rows, float* __restrict__ dst,
-                                  int D) {
-    pdl_trigger();
-    pdl_wait();
-    const float* s = src + (size_t)rows[blockIdx.x] * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[(size_t)blockIdx.x * D + i] = s[i];
-}
-__global__ void k_decode_advance(int32_t* __restrict__ tokens, int32_t* __restrict__ pos, const int32_t* __restrict__ next,
-                                 int B) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < B) {
-        tokens[i] = next[i];
-        pos[i] += 1;
-    }
-}
-__global__ void k_iota_i32(int32_t* a, int32_t* b, int n) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) a[i] = b[i] = i;
-}
-
-// staged (rows, cols) tensor of bfloat16 (elem 2) or float32 (elem 4) -> new device array of float / the activation type
-template <typename TD>
-int convert_to(zl_dekipel* m, const Staged* s, TD* dst, size_t n) {
-    const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (s->elem == 2)
-        k_convert<__nv_bfloat16, TD><<<blocks, 256, 0, m->stream>>>(static_cast<const __nv_bfloat16*>(s->ptr), dst, n);
-    else
-        k_convert<float, TD><<<blocks, 256, 0, m->stream>>>(static_cast<const float*>(s->ptr), dst, n);
-    ZL_CHECK_LAUNCH();
-    return ZL_OK;
-}
-
-const Staged* need(zl_dekipel* m, const std::string& name, int rows, int cols) {
-    const Staged* s = staged_find(m->staged, name);
-    if (!s || (size_t)s->rows * s->cols != (size_t)rows * cols || (s->elem != 2 && s->elem != 4) ||
-        (s->rows != rows && !(rows == 1 || cols == 1))) {
-        zl_set_last_error(__FILE__, __LINE__, ("missing or ill-shaped tensor " + name).c_str());
-        return nullptr;
-    }
-    return s;
-}
-
-int take_f32(zl_dekipel* m, const std::string& name, int rows, int cols, float** out) {
-    const Staged* s = need(m, name, rows, cols);
-    if (!s) return ZL_ERR_STATE;
-    const size_t n = (size_t)rows * cols;
-    RCHECK(dmalloc((void**)out, n * 4));
-    RCHECK(convert_to<float>(m, s, *out, n));
-    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
-    staged_drop(m->staged, name);
-    m->weight_bytes += (double)n * 4;
-    return ZL_OK;
-}
-
-// convert into dst (activation dtype) at element offset `off`
-int put_weight(zl_dekipel* m, const std::string& name, int rows, int cols, void* dst, size_t off) {
-    const Staged* s = need(m, name, rows, cols);
-    if (!s) return ZL_ERR_STATE;
-    const size_t n = (size_t)rows * cols;
-    if (m->cfg.dtype == ZL_F32)
-        RCHECK(convert_to<float>(m, s, static_cast<float*>(dst) + off, n));
-    else
-        RCHECK(convert_to<__nv_bfloat16>(m, s, static_cast<__nv_bfloat16*>(dst) + off, n));
-    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
-    staged_drop(m->staged, name);
-    m->weight_bytes += (double)n * m->esz;
-    return ZL_OK;
-}
-
-int take_weight(zl_dekipel* m, const std::string& name, int rows, int cols, void** out) {
-    RCHECK(dmalloc(out, (size_t)rows * cols * m->esz));
-    return put_weight(m, name, rows, cols, *out, 0);
-}
-
 int finalize_layer(zl_dekipel* m, int l) {
     const auto& c = m->cfg;
     DLayer& L = m->layers[l];
@@ -329,10 +241,10 @@ int enqueue_step(zl_dekipel* m, int T, int n_want, int max_len) {
     static const bool fuse = getenv("ZL_DEKIPEL_UNFUSED") == nullptr;
     if (dt == ZL_F32)
         ZL_CHECK_CUDA(launch(k_embed_f32<float>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
-                             (const float*)m->embed, m->x, D, c.vocab));
+                             (const float*)m->embed, m->x, D, c.vocab, 1.0f));
     else
         ZL_CHECK_CUDA(launch(k_embed_f32<__nv_bfloat16>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
-                             (const __nv_bfloat16*)m->embed, m->x, D, c.vocab));
+                             (const __nv_bfloat16*)m->embed, m->x, D, c.vocab, 1.0f));
     for (int l = 0; l < c.num_layers; ++l) {
         DLayer& L = m->layers[l];
         const auto& lc = L.c;
@@ -413,21 +325,6 @@ int run_step(zl_dekipel* m, int T, int n_want, int max_len) {
         it = m->graphs.emplace(key, exec).first;
     }
     ZL_CHECK_CUDA(cudaGraphLaunch(it->second, m->stream));
-    return ZL_OK;
-}
-
-int stage_random(zl_dekipel* m, const std::string& name, int rows, int cols, float lo, float hi, uint64_t seed) {
-    Staged s;
-    s.rows = rows;
-    s.cols = cols;
-    s.elem = 2;
-    const size_t n = (size_t)rows * cols;
-    RCHECK(dmalloc(&s.ptr, n * 2));
-    uint64_t h = seed;
-    for (char ch : name) h = h * 1099511628211ull + (unsigned char)ch;
-    RCHECK(zl_fill_uniform(s.ptr, n, lo, hi, h, ZL_BF16, m->stream));
-    staged_drop(m->staged, name);
-    m->staged[name] = s;
     return ZL_OK;
 }
 

@@ -1,5 +1,9 @@
 // General tiled GEMM y[b](M,N) = epi(x[b](M,K) @ w[b](N,K)^T) for any M, N, K, with a batch of strided problems
-// (one per attention head) and small fused epilogues.
+// (one per attention head) and small fused epilogues: a per-column bias, relu^2, tanh, a sigmoid gate, and the clamped
+// gated unit of expert feed-forwards (columns 2j / 2j+1 hold gate / up, output column j).  Grouped mode serves
+// mixtures of experts: problem b owns the rows grp_off[b] .. grp_off[b+1] of a list sorted by expert, input rows are
+// gathered and output rows scattered through index lists, so one launch covers every expert of a step whatever
+// the routing turned out to be (the counts stay on the device: the launch can sit in a CUDA graph).
 //
 // The decode-sized dense Linear of the framework (dense_gemm.cu) wants K % 32 == 0 and M <= 32 per pass and re-streams
 // the weights for every 32 rows; models whose projection ranks are not multiples of 32, prompt-sized M, and per-head
@@ -17,7 +21,28 @@ struct GemmP {
     const float* gate;
     long long ldx, xb, ldw, wb, ldy, yb, ldg, gb;
     int M, N, K;
+    const float* bias = nullptr;      // (batch, N) fp32, added before the epilogue
+    long long bb = 0;
+    const int32_t* grp_off = nullptr; // grouped mode: rows grp_off[b] .. grp_off[b+1] of the sorted list belong to problem b
+    const int32_t* x_rows = nullptr;  // sorted index -> row of x (identity when null)
+    const int32_t* y_rows = nullptr;  // sorted index -> row of y (identity when null)
+    float limit = 0.f, alpha = 1.f, beta = 0.f;   // gated unit: g = min(gate, limit), u = clamp(up, +-limit), g sigmoid(alpha g) (u + beta)
 };
+
+// rows of problem b and the place of its first row in the sorted list
+__device__ __forceinline__ void gemm_rows_of(const GemmP& p, int b, int& rows, int& first) {
+    if (p.grp_off) {
+        first = p.grp_off[b];
+        rows = p.grp_off[b + 1] - first;
+    } else {
+        first = 0;
+        rows = p.M;
+    }
+}
+__device__ __forceinline__ float glu_clamp(float gate, float up, const GemmP& p) {
+    const float g = fminf(gate, p.limit), u = fminf(fmaxf(up, -p.limit), p.limit);
+    return g * (1.0f / (1.0f + expf(-p.alpha * g))) * (u + p.beta);
+}
 
 template <int EPI>
 __device__ __forceinline__ float gemm_epilogue(float v, const GemmP& p, int b, int m, int n) {
@@ -27,6 +52,8 @@ __device__ __forceinline__ float gemm_epilogue(float v, const GemmP& p, int b, i
     } else if constexpr (EPI == ZL_GEMM_EPI_SIGMOID_GATE) {
         const float g = p.gate[(size_t)b * p.gb + (size_t)m * p.ldg + n];
         return v * (1.0f / (1.0f + expf(-g)));
+    } else if constexpr (EPI == ZL_GEMM_EPI_TANH) {
+        return tanhf(v);
     } else {
         return v;
     }
@@ -73,16 +100,16 @@ __device__ __forceinline__ void g_ldmatrix_x4(uint32_t (&r)[4], const void* smem
                  : "r"(smem_u32(smem_row)));
 }
 
-// one 64 x 32 tile of a row-major (rows, K) matrix into shared memory: 16-byte cp.async pieces when the layout allows,
-// guarded element loads otherwise; rows / k beyond the matrix become zeros
+// one 64 x 32 tile into shared memory from the two row pointers of this thread (null: a row beyond the matrix): 16-byte
+// cp.async pieces when the layout allows, guarded element loads otherwise; rows / k beyond the matrix become zeros
 template <typename T>
-__device__ __forceinline__ void stage_tile(T (*dst)[kGK + kGPad], const T* base, long long ld, int row0, int rows, int k0,
-                                           int K, bool vec, int lr, int lc) {
+__device__ __forceinline__ void stage_tile(T (*dst)[kGK + kGPad], const T* const (&rowp)[2], int k0, int K, bool vec, int lr,
+                                           int lc) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-        const int r = lr + half * 32, row = row0 + r, k = k0 + lc;
-        if (vec && row < rows && k < K) g_cp_async16(&dst[r][lc], base + (size_t)row * ld + k);
-        else *reinterpret_cast<uint4*>(&dst[r][lc]) = load8(base, ld, row, rows, k, K, false);
+        const int r = lr + half * 32, k = k0 + lc;
+        if (vec && rowp[half] && k < K) g_cp_async16(&dst[r][lc], rowp[half] + k);
+        else *reinterpret_cast<uint4*>(&dst[r][lc]) = load8(rowp[half], 0, 0, rowp[half] ? 1 : 0, k, K, false);
     }
 }
 
@@ -98,6 +125,9 @@ __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int lr = tid >> 2, lc = (tid & 3) * 8;   // this thread's 8-element pieces: rows lr and lr + 32
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const T* wrow[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) wrow[half] = n0 + lr + half * 32 < p.N ? w + (size_t)(n0 + lr + half * 32) * p.ldw : nullptr;
     float acc[2][4][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
@@ -108,10 +138,19 @@ __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w)
 
     const int steps = cdiv(p.K, kGK);
     pdl_wait();
+    int M, first;
+    gemm_rows_of(p, b, M, first);   // the index lists are a predecessor's output: read after the wait
+    if (m0 >= M) return;
+    const T* xrow[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int m = m0 + lr + half * 32;
+        xrow[half] = m < M ? x + (size_t)(p.x_rows ? p.x_rows[first + m] : first + m) * p.ldx : nullptr;
+    }
     for (int s = 0; s < kGStages - 1; ++s) {
         if (s < steps) {
-            stage_tile<T>(sA[s], x, p.ldx, m0, p.M, s * kGK, p.K, vec_x, lr, lc);
-            stage_tile<T>(sB[s], w, p.ldw, n0, p.N, s * kGK, p.K, vec_w, lr, lc);
+            stage_tile<T>(sA[s], xrow, s * kGK, p.K, vec_x, lr, lc);
+            stage_tile<T>(sB[s], wrow, s * kGK, p.K, vec_w, lr, lc);
         }
         g_cp_commit();
     }
@@ -121,8 +160,8 @@ __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w)
         __syncthreads();             // ... for every thread; and every warp is done with tile s - 1, whose buffer is refilled now
         if (s + kGStages - 1 < steps) {
             const int nb = (s + kGStages - 1) % kGStages, k0 = (s + kGStages - 1) * kGK;
-            stage_tile<T>(sA[nb], x, p.ldx, m0, p.M, k0, p.K, vec_x, lr, lc);
-            stage_tile<T>(sB[nb], w, p.ldw, n0, p.N, k0, p.K, vec_w, lr, lc);
+            stage_tile<T>(sA[nb], xrow, k0, p.K, vec_x, lr, lc);
+            stage_tile<T>(sB[nb], wrow, k0, p.K, vec_w, lr, lc);
         }
         g_cp_commit();
 #pragma unroll
@@ -141,16 +180,30 @@ __global__ void __launch_bounds__(128) k_gemm_mma(GemmP p, int vec_x, int vec_w)
         }
     }
     TO* y = static_cast<TO*>(p.y) + (size_t)b * p.yb;
+    const float* bias = p.bias ? p.bias + (size_t)b * p.bb : nullptr;
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int hh = 0; hh < 2; ++hh) {
+            const int m = m0 + wm + i * 16 + g + hh * 8;
+            if (m >= M) continue;
+            const size_t yr = (size_t)(p.y_rows ? p.y_rows[first + m] : first + m) * p.ldy;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int m = m0 + wm + i * 16 + g + ((c >> 1) ? 8 : 0);
-                const int n = n0 + wn + j * 8 + 2 * t + (c & 1);
-                if (m < p.M && n < p.N) y[(size_t)m * p.ldy + n] = from_f32<TO>(gemm_epilogue<EPI>(acc[i][j][c], p, b, m, n));
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + wn + j * 8 + 2 * t;
+                float v0 = acc[i][j][hh * 2], v1 = acc[i][j][hh * 2 + 1];
+                if (bias) {
+                    if (n < p.N) v0 += bias[n];
+                    if (n + 1 < p.N) v1 += bias[n + 1];
+                }
+                if constexpr (EPI == ZL_GEMM_EPI_GLU_CLAMP) {
+                    if (n + 1 < p.N) y[yr + (n >> 1)] = from_f32<TO>(glu_clamp(v0, v1, p));
+                } else {
+                    if (n < p.N) y[yr + n] = from_f32<TO>(gemm_epilogue<EPI>(v0, p, b, m, n));
+                    if (n + 1 < p.N) y[yr + n + 1] = from_f32<TO>(gemm_epilogue<EPI>(v1, p, b, m, n + 1));
+                }
             }
+        }
 }
 
 
@@ -201,6 +254,7 @@ __global__ void __launch_bounds__(256) k_gemm_small_m(GemmP p) {
         }
         if (lane < p.M) {
             TO* y = static_cast<TO*>(p.y) + (size_t)b * p.yb;
+            if (p.bias) mine += p.bias[(size_t)b * p.bb + n];
             y[(size_t)lane * p.ldy + n] = from_f32<TO>(gemm_epilogue<EPI>(mine, p, b, lane, n));
         }
     }
@@ -218,16 +272,17 @@ template <typename T, typename TO>
 static cudaError_t launch_small_m(const GemmP& p, int batch, int epi, bool pdl, cudaStream_t st) {
     if (epi == ZL_GEMM_EPI_RELU2) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_RELU2>(p, batch, pdl, st);
     if (epi == ZL_GEMM_EPI_SIGMOID_GATE) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_SIGMOID_GATE>(p, batch, pdl, st);
+    if (epi == ZL_GEMM_EPI_TANH) return launch_small_m_mt<T, TO, ZL_GEMM_EPI_TANH>(p, batch, pdl, st);
     return launch_small_m_mt<T, TO, ZL_GEMM_EPI_NONE>(p, batch, pdl, st);
 }
 
 // ---- fp32 inputs ---------------------------------------------------------------------------------------------------
 constexpr int kFK = 16;
 
-__device__ __forceinline__ float4 load4f(const float* base, long long ld, int row, int rows, int k, int K, bool vec) {
+__device__ __forceinline__ float4 load4f(const float* rowp, int k, int K, bool vec) {
     float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row >= rows || k >= K) return r;
-    const float* p = base + (size_t)row * ld + k;
+    if (!rowp || k >= K) return r;
+    const float* p = rowp + k;
     if (vec) return *reinterpret_cast<const float4*>(p);
     r.x = p[0];
     if (k + 1 < K) r.y = p[1];
@@ -252,9 +307,14 @@ __global__ void __launch_bounds__(256) k_gemm_f32(GemmP p, int vec_x, int vec_w)
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    float4 rw = load4f(w, p.ldw, n0 + lr, p.N, lc, p.K, vec_w);
+    const float* wrow = n0 + lr < p.N ? w + (size_t)(n0 + lr) * p.ldw : nullptr;
+    float4 rw = load4f(wrow, lc, p.K, vec_w);
     pdl_wait();
-    float4 rx = load4f(x, p.ldx, m0 + lr, p.M, lc, p.K, vec_x);
+    int M, first;
+    gemm_rows_of(p, b, M, first);
+    if (m0 >= M) return;
+    const float* xrow = m0 + lr < M ? x + (size_t)(p.x_rows ? p.x_rows[first + m0 + lr] : first + m0 + lr) * p.ldx : nullptr;
+    float4 rx = load4f(xrow, lc, p.K, vec_x);
     const int steps = cdiv(p.K, kFK);
     for (int s = 0; s < steps; ++s) {
         __syncthreads();   // the previous step's reads are done
@@ -263,8 +323,8 @@ __global__ void __launch_bounds__(256) k_gemm_f32(GemmP p, int vec_x, int vec_w)
         __syncthreads();
         if (s + 1 < steps) {
             const int k = (s + 1) * kFK + lc;
-            rx = load4f(x, p.ldx, m0 + lr, p.M, k, p.K, vec_x);
-            rw = load4f(w, p.ldw, n0 + lr, p.N, k, p.K, vec_w);
+            rx = load4f(xrow, k, p.K, vec_x);
+            rw = load4f(wrow, k, p.K, vec_w);
         }
 #pragma unroll
         for (int k = 0; k < kFK; ++k) {
@@ -278,13 +338,31 @@ __global__ void __launch_bounds__(256) k_gemm_f32(GemmP p, int vec_x, int vec_w)
         }
     }
     float* y = static_cast<float*>(p.y) + (size_t)b * p.yb;
+    const float* bias = p.bias ? p.bias + (size_t)b * p.bb : nullptr;
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+        const size_t yr = (size_t)(p.y_rows ? p.y_rows[first + m] : first + m) * p.ldy;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-            if (m < p.M && n < p.N) y[(size_t)m * p.ldy + n] = gemm_epilogue<EPI>(acc[i][j], p, b, m, n);
+            const int n = n0 + tx * 4 + j;
+            if (bias && n < p.N) acc[i][j] += bias[n];
         }
+        if constexpr (EPI == ZL_GEMM_EPI_GLU_CLAMP) {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < p.N) y[yr + (n >> 1)] = glu_clamp(acc[i][j], acc[i][j + 1], p);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + tx * 4 + j;
+                if (n < p.N) y[yr + n] = gemm_epilogue<EPI>(acc[i][j], p, b, m, n);
+            }
+        }
+    }
 }
 
 template <typename T, typename TO>
@@ -293,6 +371,9 @@ static cudaError_t launch_mma(const GemmP& p, int batch, int epi, bool vx, bool 
     if (epi == ZL_GEMM_EPI_RELU2) return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_RELU2>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
     if (epi == ZL_GEMM_EPI_SIGMOID_GATE)
         return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_SIGMOID_GATE>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+    if (epi == ZL_GEMM_EPI_TANH) return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_TANH>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
+    if (epi == ZL_GEMM_EPI_GLU_CLAMP)
+        return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_GLU_CLAMP>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
     return launch(k_gemm_mma<T, TO, ZL_GEMM_EPI_NONE>, grid, block, 0, st, pdl, p, (int)vx, (int)vw);
 }
 
@@ -306,20 +387,21 @@ static bool aligned_for(const void* ptr, long long ld, long long bstride, int K,
 
 using namespace zl;
 
-extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride, const void* w, long long ldw,
-                          long long w_batch_stride, void* y, long long ldy, long long y_batch_stride, int M, int N, int K,
-                          int batch, int in_dtype, int out_dtype, int epilogue, const float* gate, long long ldg,
-                          long long gate_batch_stride, int pdl, zl_stream_t stream) {
-    ZL_CHECK_ARG(x && w && y && M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535);
-    ZL_CHECK_ARG(ldx >= K && ldw >= K && ldy >= N);
+static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int epilogue, int pdl, cudaStream_t stream) {
+    const int M = p.M, N = p.N, K = p.K;
+    const bool grouped = p.grp_off != nullptr, pairs = epilogue == ZL_GEMM_EPI_GLU_CLAMP;
+    ZL_CHECK_ARG(p.x && p.w && p.y && M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535);
+    ZL_CHECK_ARG(p.ldx >= K && p.ldw >= K && p.ldy >= (pairs ? N / 2 : N));
     ZL_CHECK_ARG(in_dtype == ZL_F16 || in_dtype == ZL_BF16 || in_dtype == ZL_F32);
     ZL_CHECK_ARG(out_dtype == in_dtype || out_dtype == ZL_F32);
-    ZL_CHECK_ARG(epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_RELU2 || epilogue == ZL_GEMM_EPI_SIGMOID_GATE);
-    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_SIGMOID_GATE || (gate && ldg >= N));
+    ZL_CHECK_ARG(epilogue >= ZL_GEMM_EPI_NONE && epilogue <= ZL_GEMM_EPI_GLU_CLAMP);
+    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_SIGMOID_GATE || (p.gate && p.ldg >= N && !grouped));
+    ZL_CHECK_ARG(!pairs || N % 2 == 0);
+    ZL_CHECK_ARG(grouped || (!p.x_rows && !p.y_rows));
     ZL_CHECK_ARG(cdiv(M, kGB) <= 65535 && cdiv(N, kSmCols) <= 2147483647);
-    GemmP p{x, w, y, gate, ldx, x_batch_stride, ldw, w_batch_stride, ldy, y_batch_stride, ldg, gate_batch_stride, M, N, K};
     const int elem = in_dtype == ZL_F32 ? 4 : 2;
-    const bool vx = aligned_for(x, ldx, x_batch_stride, K, elem, batch), vw = aligned_for(w, ldw, w_batch_stride, K, elem, batch);
+    // gathered rows start at any multiple of ldx: the batch stride plays no part in their alignment
+    const bool vx = aligned_for(p.x, p.ldx, p.xb, K, elem, batch), vw = aligned_for(p.w, p.ldw, p.wb, K, elem, batch);
     cudaError_t e;
     if (in_dtype == ZL_F32) {
         const dim3 grid(cdiv(N, kGB), cdiv(M, kGB), batch), block(256);
@@ -327,9 +409,13 @@ extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride
             e = launch(k_gemm_f32<ZL_GEMM_EPI_RELU2>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
         else if (epilogue == ZL_GEMM_EPI_SIGMOID_GATE)
             e = launch(k_gemm_f32<ZL_GEMM_EPI_SIGMOID_GATE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+        else if (epilogue == ZL_GEMM_EPI_TANH)
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_TANH>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+        else if (epilogue == ZL_GEMM_EPI_GLU_CLAMP)
+            e = launch(k_gemm_f32<ZL_GEMM_EPI_GLU_CLAMP>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
         else
             e = launch(k_gemm_f32<ZL_GEMM_EPI_NONE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
-    } else if (M <= 8 && vx && vw && (size_t)M * K * 2 <= 48 * 1024) {   // few rows: stream the weights once per column
+    } else if (!grouped && !pairs && M <= 8 && vx && vw && (size_t)M * K * 2 <= 48 * 1024) {   // few rows: stream the weights once per column
         if (in_dtype == ZL_BF16)
             e = out_dtype == ZL_F32 ? launch_small_m<__nv_bfloat16, float>(p, batch, epilogue, pdl != 0, stream)
                                     : launch_small_m<__nv_bfloat16, __nv_bfloat16>(p, batch, epilogue, pdl != 0, stream);
@@ -345,4 +431,38 @@ extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride
     }
     ZL_CHECK_CUDA(e);
     return ZL_OK;
+}
+
+extern "C" int zl_gemm_nt(const void* x, long long ldx, long long x_batch_stride, const void* w, long long ldw,
+                          long long w_batch_stride, void* y, long long ldy, long long y_batch_stride, int M, int N, int K,
+                          int batch, int in_dtype, int out_dtype, int epilogue, const float* gate, long long ldg,
+                          long long gate_batch_stride, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(epilogue != ZL_GEMM_EPI_GLU_CLAMP);
+    GemmP p{x, w, y, gate, ldx, x_batch_stride, ldw, w_batch_stride, ldy, y_batch_stride, ldg, gate_batch_stride, M, N, K};
+    return gemm_dispatch(p, batch, in_dtype, out_dtype, epilogue, pdl, stream);
+}
+
+extern "C" int zl_gemm_nt_bias(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* y,
+                               long long ldy, int M, int N, int K, int in_dtype, int out_dtype, int epilogue, int pdl,
+                               zl_stream_t stream) {
+    ZL_CHECK_ARG(epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_RELU2 || epilogue == ZL_GEMM_EPI_TANH);
+    GemmP p{x, w, y, nullptr, ldx, 0, ldw, 0, ldy, 0, 0, 0, M, N, K};
+    p.bias = bias;
+    return gemm_dispatch(p, 1, in_dtype, out_dtype, epilogue, pdl, stream);
+}
+
+extern "C" int zl_gemm_nt_grouped(const void* x, long long ldx, const int32_t* x_rows, const void* w, long long ldw,
+                                  long long w_group_stride, void* y, long long ldy, const int32_t* y_rows,
+                                  const int32_t* group_offsets, int groups, int max_rows, int N, int K, int in_dtype,
+                                  int out_dtype, int epilogue, float limit, float alpha, float beta, int pdl,
+                                  zl_stream_t stream) {
+    ZL_CHECK_ARG(group_offsets && (epilogue == ZL_GEMM_EPI_NONE || epilogue == ZL_GEMM_EPI_GLU_CLAMP));
+    GemmP p{x, w, y, nullptr, ldx, 0, ldw, w_group_stride, ldy, 0, 0, 0, max_rows, N, K};
+    p.grp_off = group_offsets;
+    p.x_rows = x_rows;
+    p.y_rows = y_rows;
+    p.limit = limit;
+    p.alpha = alpha;
+    p.beta = beta;
+    return gemm_dispatch(p, groups, in_dtype, out_dtype, epilogue, pdl, stream);
 }

@@ -1,0 +1,119 @@
+// Routing of a mixture of experts, on the device from the router's input to the index lists of the grouped GEMMs:
+//   * k_moe_route: logits z = W_router x in fp32 (x is the fp32 residual stream), a score per expert (sigmoid or
+//     softmax over the experts), the `top` experts with the largest score + correction (ties: the lower index), their
+//     weights = the scores without the correction, optionally renormalised to sum 1;
+//   * k_moe_plan: the (token, choice) pairs sorted by expert: group offsets, and for every list entry the token row it
+//     reads and the pair row it writes.  The order inside a group is arbitrary (no row's result depends on it).
+// Nothing returns to the host, so a step with routing can be captured in a CUDA graph.
+#include "common.cuh"
+
+namespace zl {
+
+// grid (T), 128 threads; dynamic shared memory 2 * E floats
+__global__ void __launch_bounds__(128) k_moe_route(const float* __restrict__ x, long long ldx,
+                                                   const float* __restrict__ w_router, const float* __restrict__ correction,
+                                                   int32_t* __restrict__ top_e, float* __restrict__ top_w, int D, int E,
+                                                   int top, int score_fn, int renorm) {
+    extern __shared__ float sm[];
+    float* score = sm;        // s_e
+    float* choice = sm + E;   // s_e + correction_e; taken experts drop to -inf
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* xr = x + (size_t)t * ldx;
+    for (int e = warp; e < E; e += 4) {
+        const float* wr = w_router + (size_t)e * D;
+        float acc = 0.f;
+        for (int c = lane; c < D; c += 32) acc = fmaf(xr[c], wr[c], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) score[e] = acc;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (score_fn == ZL_MOE_SCORE_SOFTMAX) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, score[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += expf(score[e] - mx);
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) score[e] = expf(score[e] - mx) / sum;
+    } else {
+        for (int e = lane; e < E; e += 32) score[e] = 1.0f / (1.0f + expf(-score[e]));
+    }
+    for (int e = lane; e < E; e += 32) choice[e] = score[e] + (correction ? correction[e] : 0.f);
+    __syncwarp();
+    float wsum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = choice[e];
+            if (v > bv) bv = v, bi = e;   // ascending e: the lower index wins a tie inside a lane
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+        }
+        if (bi >= E) bi = k < E ? k : 0;   // only when every score is NaN / -inf
+        if (lane == 0) {
+            top_e[(size_t)t * top + k] = bi;
+            top_w[(size_t)t * top + k] = score[bi];
+            choice[bi] = -INFINITY;
+        }
+        wsum += score[bi];
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int k = 0; k < top; ++k) top_w[(size_t)t * top + k] /= wsum;
+}
+
+// one CTA; dynamic shared memory 2 * (E + 1) ints
+__global__ void __launch_bounds__(1024) k_moe_plan(const int32_t* __restrict__ top_e, int pairs, int E, int top,
+                                                   int32_t* __restrict__ grp_off, int32_t* __restrict__ list_token,
+                                                   int32_t* __restrict__ list_pair) {
+    extern __shared__ int ism[];
+    int* cnt = ism;            // E + 1
+    int* cur = ism + E + 1;    // E + 1
+    pdl_trigger();
+    pdl_wait();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&cnt[top_e[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = cnt[e];
+            cur[e] = run;
+            grp_off[e] = run;
+            run += c;
+        }
+        grp_off[E] = run;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int at = atomicAdd(&cur[top_e[i]], 1);
+        list_token[at] = i / top;
+        list_pair[at] = i;
+    }
+}
+
+}  // namespace zl
+
+using namespace zl;
+
+extern "C" int zl_moe_route(const float* x, long long ldx, const float* w_router, const float* correction, int32_t* top_experts,
+                            float* top_weights, int32_t* group_offsets, int32_t* list_token, int32_t* list_pair, int T, int D,
+                            int experts, int top, int score_fn, int renormalize, int pdl, zl_stream_t stream) {
+    ZL_CHECK_ARG(x && w_router && top_experts && top_weights && group_offsets && list_token && list_pair);
+    ZL_CHECK_ARG(T > 0 && D > 0 && experts > 0 && top > 0 && top <= experts && experts <= 4096);
+    ZL_CHECK_ARG(score_fn == ZL_MOE_SCORE_SIGMOID || score_fn == ZL_MOE_SCORE_SOFTMAX);
+    ZL_CHECK_CUDA(launch(k_moe_route, dim3(T), dim3(128), (size_t)2 * experts * sizeof(float), stream, pdl != 0, x, ldx, w_router,
+                         correction, top_experts, top_weights, D, experts, top, score_fn, renormalize));
+    ZL_CHECK_CUDA(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)2 * (experts + 1) * sizeof(int), stream, pdl != 0,
+                         (const int32_t*)top_experts, T * top, experts, top, group_offsets, list_token, list_pair));
+    return ZL_OK;
+}

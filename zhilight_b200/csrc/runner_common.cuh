@@ -1,19 +1,20 @@
-// Host-side pieces shared by the model drivers (llama_runner.cu, dekipel_runner.cu): staged checkpoint tensors,
+// Host-side pieces shared by the model drivers (llama_runner.cu, dekipel_runner.cu, kodupel_runner.cu): staged checkpoint tensors,
 // device allocation helpers, and the slot cache -- the per-task, per-layer row buffers every driver appends to and
 // its kernels reach through a device table of slot base pointers (the reference's per-task buffer tables,
 // src/model/rag_buffer_context.h:141-181).
 #pragma once
 #include "common.cuh"
 
+#include <cmath>
 #include <map>
 #include <string>
 #include <vector>
 
 namespace zl {
 
-#define RCHECK(expr)                  \
+#define RCHECK(...)                   \
     do {                              \
-        int _rc = (expr);             \
+        int _rc = (__VA_ARGS__);           \
         if (_rc != ZL_OK) return _rc; \
     } while (0)
 
@@ -100,5 +101,117 @@ struct SlotCache {
         addrs = nullptr;
     }
 };
+
+// ---- pieces of a driver with an fp32 residual stream ------------------------------------------------------------------
+// M is the driver's model struct: it has `staged`, `stream`, `weight_bytes`, `esz` (bytes of a weight element) and
+// `cfg.dtype`.  The embedding gather multiplies by `scale` (1 for models without an embedding scale).
+template <typename TS, typename TD>
+__global__ void k_convert(const TS* __restrict__ src, TD* __restrict__ dst, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = from_f32<TD>(to_f32<TS>(src[i]));
+}
+template <typename TW>
+__global__ void k_embed_f32(const int32_t* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out, int D,
+                            int vocab, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    int id = ids[blockIdx.x];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) out[(size_t)blockIdx.x * D + i] = to_f32<TW>(table[(size_t)id * D + i]) * scale;
+}
+static __global__ void k_gather_rows_f32(const float* __restrict__ src, const int32_t* __restrict__ rows, float* __restrict__ dst,
+                                  int D) {
+    pdl_trigger();
+    pdl_wait();
+    const float* s = src + (size_t)rows[blockIdx.x] * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[(size_t)blockIdx.x * D + i] = s[i];
+}
+static __global__ void k_decode_advance(int32_t* __restrict__ tokens, int32_t* __restrict__ pos, const int32_t* __restrict__ next,
+                                 int B) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B) {
+        tokens[i] = next[i];
+        pos[i] += 1;
+    }
+}
+static __global__ void k_iota_i32(int32_t* a, int32_t* b, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = b[i] = i;
+}
+
+// staged (rows, cols) tensor of bfloat16 (elem 2) or float32 (elem 4) -> new device array of float / the activation type
+template <typename TD, typename M>
+int convert_to(M* m, const Staged* s, TD* dst, size_t n) {
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (s->elem == 2)
+        k_convert<__nv_bfloat16, TD><<<blocks, 256, 0, m->stream>>>(static_cast<const __nv_bfloat16*>(s->ptr), dst, n);
+    else
+        k_convert<float, TD><<<blocks, 256, 0, m->stream>>>(static_cast<const float*>(s->ptr), dst, n);
+    ZL_CHECK_LAUNCH();
+    return ZL_OK;
+}
+
+template <typename M>
+const Staged* need(M* m, const std::string& name, int rows, int cols) {
+    const Staged* s = staged_find(m->staged, name);
+    if (!s || (size_t)s->rows * s->cols != (size_t)rows * cols || (s->elem != 2 && s->elem != 4) ||
+        (s->rows != rows && !(rows == 1 || cols == 1))) {
+        zl_set_last_error(__FILE__, __LINE__, ("missing or ill-shaped tensor " + name).c_str());
+        return nullptr;
+    }
+    return s;
+}
+
+template <typename M>
+int take_f32(M* m, const std::string& name, int rows, int cols, float** out) {
+    const Staged* s = need(m, name, rows, cols);
+    if (!s) return ZL_ERR_STATE;
+    const size_t n = (size_t)rows * cols;
+    RCHECK(dmalloc((void**)out, n * 4));
+    RCHECK(convert_to<float>(m, s, *out, n));
+    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
+    staged_drop(m->staged, name);
+    m->weight_bytes += (double)n * 4;
+    return ZL_OK;
+}
+
+// convert into dst (activation dtype) at element offset `off`
+template <typename M>
+int put_weight(M* m, const std::string& name, int rows, int cols, void* dst, size_t off) {
+    const Staged* s = need(m, name, rows, cols);
+    if (!s) return ZL_ERR_STATE;
+    const size_t n = (size_t)rows * cols;
+    if (m->cfg.dtype == ZL_F32)
+        RCHECK(convert_to<float>(m, s, static_cast<float*>(dst) + off, n));
+    else
+        RCHECK(convert_to<__nv_bfloat16>(m, s, static_cast<__nv_bfloat16*>(dst) + off, n));
+    ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
+    staged_drop(m->staged, name);
+    m->weight_bytes += (double)n * m->esz;
+    return ZL_OK;
+}
+
+template <typename M>
+int take_weight(M* m, const std::string& name, int rows, int cols, void** out) {
+    RCHECK(dmalloc(out, (size_t)rows * cols * m->esz));
+    return put_weight(m, name, rows, cols, *out, 0);
+}
+
+template <typename M>
+int stage_random(M* m, const std::string& name, int rows, int cols, float lo, float hi, uint64_t seed) {
+    Staged s;
+    s.rows = rows;
+    s.cols = cols;
+    s.elem = 2;
+    const size_t n = (size_t)rows * cols;
+    RCHECK(dmalloc(&s.ptr, n * 2));
+    uint64_t h = seed;
+    for (char ch : name) h = h * 1099511628211ull + (unsigned char)ch;
+    RCHECK(zl_fill_uniform(s.ptr, n, lo, hi, h, ZL_BF16, m->stream));
+    staged_drop(m->staged, name);
+    m->staged[name] = s;
+    return ZL_OK;
+}
+
 
 }  // namespace zl

@@ -74,6 +74,16 @@ def _build_dekipel(config, dtype, max_batch, max_seq, max_step_tokens, **kw):
 register("Dekipel", _build_dekipel, ("bfloat16", "float32"))
 
 
+# ---- Kodupel ---------------------------------------------------------------------------------------------------------
+def _build_kodupel(config, dtype, max_batch, max_seq, max_step_tokens, **kw):
+    from .kodupel import KodupelDecoder
+    return KodupelDecoder.from_config_dict(config, dtype=dtype, max_batch=max_batch, max_seq=max_seq,
+                                           max_step_tokens=max_step_tokens, **kw)
+
+
+register("Kodupel", _build_kodupel, ("bfloat16", "float32"))
+
+
 # ---- Llama (HF folder) -----------------------------------------------------------------------------------------------
 _HF_LLAMA_NAMES = [
     (r"^model\.embed_tokens\.weight$", "token_embedding.weight"),
