@@ -434,6 +434,141 @@ def run_compare_dekipel(args):
                       "timing": "CUDA events on the model's stream; weights per pass larger than L2"}))
 
 
+# ----------------------------------------------------------------------------------------------------------------------
+# --compare-kodupel: prefill and decode throughput of the Kodupel family beside the bf16 Llama decoder (the closest
+# existing model: grouped-query attention with cached keys and values and a gated feed-forward) at equal width, depth,
+# heads and equal active Linear parameters per token, random weights.  Does not touch the default workload.
+# ----------------------------------------------------------------------------------------------------------------------
+KODUPEL_SIZES = {
+    # Llama: 8 key/value heads, dense ff.  Kodupel: layers attention / attention on the first one's cache / delta rule /
+    # attention; `experts` experts of size ff_e of which `top` are used, top * ff_e = Llama's ff.
+    "1b-like": dict(width=2048, heads=16, dim=128, layers=4, vocab=32768, ff=8192, experts=16, top=4, ff_e=2048,
+                    delta_heads=16, delta_dim=64, decay_rank=64),
+    "8b-like": dict(width=4096, heads=32, dim=128, layers=4, vocab=32768, ff=14336, experts=16, top=4, ff_e=3584,
+                    delta_heads=32, delta_dim=64, decay_rank=64),
+}
+
+
+def _kodupel_config(sz):
+    moe = {"kind": "moe", "expert": {"ff": sz["ff_e"], "limit": 7.0}, "router": {"experts": sz["experts"], "top": sz["top"]}}
+    att = dict(heads=sz["heads"], kv_heads=8, dim=sz["dim"], vdim=sz["dim"], scale=sz["dim"] ** -0.5,
+               rot={"base": 1e6, "dims": sz["dim"] // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}})
+    layers = []
+    for i in range(sz["layers"]):
+        if i % 4 == 2:
+            layers.append({"type": "general_delta", "mlp": moe,
+                           "mixer": dict(heads=sz["delta_heads"], dim=sz["delta_dim"], decay_rank=sz["decay_rank"])})
+        else:
+            mx = dict(att)
+            if i % 4 == 1:
+                mx["kv_from"] = i - 1
+            layers.append({"type": "attention", "mixer": mx, "mlp": moe})
+    return {"architecture": "Kodupel", "vocab": sz["vocab"], "width": sz["width"], "layers": layers, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}}
+
+
+def _kodupel_params(sz, rows):
+    """(Linear parameters one token uses, parameters a step of `rows` tokens reads, cache bytes per cached position,
+    state bytes per request and step)."""
+    D, H, d = sz["width"], sz["heads"], sz["dim"]
+    E, top, fe = sz["experts"], sz["top"], sz["ff_e"]
+    hd = sz["delta_heads"] * sz["delta_dim"]
+    active = read = cache = state = 0
+    touched = E * (1.0 - (1.0 - top / E) ** rows)       # expected number of distinct experts a step reads
+    for i in range(sz["layers"]):
+        if i % 4 == 2:
+            mix = 5 * hd * D + sz["decay_rank"] * (D + hd) + hd * D
+            state += 2 * sz["delta_heads"] * sz["delta_dim"] ** 2 * 4
+        else:
+            own = i % 4 != 1
+            mix = D * (H * d + (2 * 8 * d if own else 0) + H) + H * d * D
+            cache += 2 * 8 * d * 2
+        active += mix + E * D + top * 3 * D * fe
+        read += mix + E * D + touched * 3 * D * fe
+    return active + sz["vocab"] * D, read + sz["vocab"] * D, cache, state
+
+
+def run_compare_kodupel(args):
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(0)
+    from zhilight_b200 import build
+    build.build()
+    from zhilight_b200.kodupel import KodupelDecoder
+    from zhilight_b200.llama import LlamaDecoder
+    hbm, how = read_peaks()
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tflops = json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0
+    ctx, chunk, n_prompt = args.prompt if args.prompt > 128 else 1024, 1024, 2048
+    steps, warm = max(args.steps, 16), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    rows = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark_region_start()
+    for name, sz in KODUPEL_SIZES.items():
+        if args.compare_sizes and name not in args.compare_sizes.split(","):
+            continue
+        for kind in [k for k in ("kodupel", "llama") if k in args.compare_models.split(",")]:
+            max_seq = max(ctx, n_prompt) + 4 * (steps + warm) + 64
+            if kind == "kodupel":
+                dec = KodupelDecoder.from_config_dict(_kodupel_config(sz), dtype="bf16", max_batch=32, max_seq=max_seq,
+                                                      max_step_tokens=chunk, use_pdl=not args.no_pdl,
+                                                      use_graph=not args.no_graph)
+            else:
+                dec = LlamaDecoder(num_layers=sz["layers"], dim_model=sz["width"], num_heads=sz["heads"], num_kv_heads=8,
+                                   dim_head=sz["dim"], dim_ff=sz["ff"], vocab_size=sz["vocab"], quant_type=0, dtype="bf16",
+                                   max_batch=32, max_seq=max_seq, prefill_chunk=chunk, use_pdl=not args.no_pdl,
+                                   use_graph=not args.no_graph)
+            dec.init_synthetic(seed=1)
+            stream = torch.cuda.ExternalStream(dec.stream())
+            out = {"size": name, "model": kind}
+            toks = rng.integers(0, sz["vocab"], n_prompt).astype(np.int32)
+            for _ in range(2):
+                dec.prefill(0, toks, 0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                dec.prefill(0, toks, 0)
+            e1.record(stream)
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / 3
+            if kind == "kodupel":
+                active = _kodupel_params(sz, 1)[0]
+            else:
+                active = _linear_params("llama", sz)
+            out["linear_params_per_token"] = int(active)
+            flops = 2.0 * (active - sz["vocab"] * sz["width"]) * n_prompt
+            out["prefill"] = {"tokens": n_prompt, "chunk": chunk, "ms": round(ms, 3), "tok_s": round(n_prompt / ms * 1e3),
+                              "linear_tflops": round(flops / ms / 1e9, 1),
+                              "of_measured_bf16_peak": round(flops / ms / 1e9 / tflops, 4)}
+            for b in range(32):
+                dec.prefill(b, toks[:ctx], 0)
+            for B in (1, 32):
+                dec.set_state(rng.integers(0, sz["vocab"], B).astype(np.int32), np.full(B, ctx, dtype=np.int32))
+                ms, _ = measure_decode(dec, B, steps, warm, stream, torch.cuda.synchronize)
+                mid = ctx + warm + steps // 2
+                if kind == "kodupel":
+                    _, read, cache, state = _kodupel_params(sz, B)
+                    step_bytes = read * 2 + B * (mid * cache + state)
+                else:
+                    step_bytes = active * 2 + B * mid * 2 * 8 * sz["dim"] * 2 * sz["layers"]
+                out["decode_b%d" % B] = {"ctx": ctx, "ms_per_step": round(ms / steps, 4), "tok_s": round(B * steps / ms * 1e3, 1),
+                                          "step_bytes": int(step_bytes),
+                                          "of_%s_hbm_peak" % how: round(step_bytes / (ms / steps * 1e-3) / 1e9 / hbm, 4)}
+            out["kernels_per_step"] = dec.stats()[1] if kind == "kodupel" else dec.stats(1)[1]
+            dec.close()
+            del dec
+            torch.cuda.empty_cache()
+            rows.append(out)
+            print(json.dumps(out), file=sys.stderr, flush=True)
+    clocks = sampler.finish()
+    print(json.dumps({"compare": "kodupel vs llama (bf16, random weights, synthetic tokens)", "rows": rows, "clocks": clocks,
+                      "timing": "CUDA events on the model's stream; weights per pass larger than L2"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -457,11 +592,19 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=128, help="tokens per chunked-prefill pass of the TTFT measurement")
     ap.add_argument("--fuse", type=int, default=2, help="0: one kernel per reference op; 1: +RMSNorm fused; 2: +qkv RoPE/KV epilogue")
     ap.add_argument("--compare-models", default="dekipel,llama", help="--compare-dekipel: which of the two to run")
+    ap.add_argument("--compare-sizes", default="", help="--compare-kodupel: comma-separated subset of its layer sizes")
+    ap.add_argument("--compare-kodupel", action="store_true",
+                    help="instead of the default workload: Kodupel beside the bf16 Llama decoder at a few layer sizes")
     ap.add_argument("--compare-dekipel", action="store_true",
                     help="instead of the default workload: Dekipel beside the bf16 Llama decoder at a few layer sizes")
     args = ap.parse_args()
     if args.compare_dekipel:
         run_compare_dekipel(args)
+        return
+    if args.compare_kodupel:
+        if args.compare_models == "dekipel,llama":
+            args.compare_models = "kodupel,llama"
+        run_compare_kodupel(args)
         return
 
     cfg = model_cfg(args.model)

@@ -533,13 +533,16 @@ int zl_qkv_headnorm_rope_append(const float* proj, long long ldp, int q_off, int
  * p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i)) with s = scale * q . k (sink NULL: 0, i.e. one added to the
  * denominator); out (T, heads * vdim) of `dtype`, head h times sigmoid(gate[t * ldg + h]) when gate != NULL.
  * splits > 1 cuts the keys of every token over that many CTAs (decode with long contexts); workspace of
- * zl_sink_attention_workspace_bytes. */
+ * zl_sink_attention_workspace_bytes.  With the runs of the step (run i = rows run_row0[i] .. + run_len[i]: one slot,
+ * consecutive positions; max_run_len bounds run_len) 16-bit caches go through the tensor-core kernel, which tiles
+ * the tokens of a run; run_row0 NULL: the general kernel, one CTA per (token, head). */
 size_t zl_sink_attention_workspace_bytes(int T, int heads, int vdim, int splits);
 int zl_sink_attention_splits(int T, int heads, int kv_heads, int max_len);
 int zl_sink_attention(const void* q, void* const* k_addrs, void* const* v_addrs, const int32_t* slot, const int32_t* pos,
                       const float* sink, const float* gate, long long ldg, float scale, void* out, int T, int heads,
-                      int kv_heads, int dim, int vdim, int splits, void* workspace, size_t workspace_bytes, int dtype,
-                      int pdl, zl_stream_t stream);
+                      int kv_heads, int dim, int vdim, int splits, void* workspace, size_t workspace_bytes,
+                      const int32_t* run_row0, const int32_t* run_len, int runs, int max_run_len, int dtype, int pdl,
+                      zl_stream_t stream);
 /* y[t][h] = o[t][h] / sqrt(mean(o[t][h]^2 over vdim) + eps) * weight[h * vdim + c] * sigmoid(gate[t * ldg + h * vdim + c]);
  * weight and gate may be NULL. */
 int zl_head_rmsnorm_gate(const float* o, long long ldo, const float* weight, const float* gate, long long ldg, void* y,

@@ -12,6 +12,8 @@
 // product and sum in IEEE fp32.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace zl {
 
 struct GemmP {
@@ -276,6 +278,97 @@ static cudaError_t launch_small_m(const GemmP& p, int batch, int epi, bool pdl, 
     return launch_small_m_mt<T, TO, ZL_GEMM_EPI_NONE>(p, batch, pdl, st);
 }
 
+// ---- grouped problems with few rows each (decode steps of a mixture of experts) ----------------------------------------
+// One CTA = 32 output columns of one group; the group's rows (gathered through x_rows) sit in shared memory eight at a
+// time, and a warp streams the weight row of a column -- for the gated unit the gate and the up row of the column -- once
+// per eight rows with four 16-byte loads per row in flight.  Groups without rows cost an early exit.
+template <typename T, typename TO, bool GLU>
+__global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
+    extern __shared__ __align__(16) unsigned char sx_raw[];
+    T* sx = reinterpret_cast<T*>(sx_raw);   // [8][K]
+    pdl_trigger();
+    const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* w = static_cast<const T*>(p.w) + (size_t)b * p.wb;
+    const T* x = static_cast<const T*>(p.x);
+    TO* y = static_cast<TO*>(p.y);
+    const int K = p.K, K8 = K / 8, n_out = GLU ? p.N / 2 : p.N;
+    pdl_wait();
+    int M, first;
+    gemm_rows_of(p, b, M, first);
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        const int mc = min(8, M - m0);
+        __syncthreads();   // the previous eight rows are no longer read
+        for (int i = threadIdx.x; i < mc * K8; i += blockDim.x) {
+            const int m = i / K8, k8 = i - m * K8;
+            const size_t row = p.x_rows ? p.x_rows[first + m0 + m] : first + m0 + m;
+            *reinterpret_cast<uint4*>(sx + (size_t)m * K + k8 * 8) = *reinterpret_cast<const uint4*>(x + row * p.ldx + k8 * 8);
+        }
+        __syncthreads();
+        for (int n = blockIdx.x * kSmCols + warp; n < min(n_out, (int)(blockIdx.x + 1) * kSmCols); n += 8) {
+            float acc[8], acc2[8];
+#pragma unroll
+            for (int m = 0; m < 8; ++m) acc[m] = acc2[m] = 0.f;
+            const T* wr = w + (size_t)(GLU ? 2 * n : n) * p.ldw;
+            for (int k8 = lane; k8 < K8; k8 += 128) {
+                uint4 wq[4], wq2[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const bool in = k8 + 32 * u < K8;
+                    wq[u] = in ? ld_nc_na_u4(wr + (size_t)(k8 + 32 * u) * 8) : make_uint4(0, 0, 0, 0);
+                    if (GLU) wq2[u] = in ? ld_nc_na_u4(wr + p.ldw + (size_t)(k8 + 32 * u) * 8) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (k8 + 32 * u >= K8) break;
+                    float wf[8], wf2[8];
+                    unpack8<T>(wq[u], wf);
+                    if (GLU) unpack8<T>(wq2[u], wf2);
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        if (m < mc) {
+                            float xf[8];
+                            unpack8<T>(*reinterpret_cast<const uint4*>(sx + (size_t)m * K + (size_t)(k8 + 32 * u) * 8), xf);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                acc[m] = fmaf(wf[e], xf[e], acc[m]);
+                                if (GLU) acc2[m] = fmaf(wf2[e], xf[e], acc2[m]);
+                            }
+                        }
+                    }
+                }
+            }
+            float mine = 0.f;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                float v = warp_sum(acc[m]);
+                if (GLU) v = glu_clamp(v, warp_sum(acc2[m]), p);
+                if (lane == m) mine = v;
+            }
+            if (lane < mc) {
+                const size_t yr = (size_t)(p.y_rows ? p.y_rows[first + m0 + lane] : first + m0 + lane) * p.ldy;
+                y[yr + n] = from_f32<TO>(mine);
+            }
+        }
+    }
+}
+
+template <typename T, typename TO>
+static cudaError_t launch_grouped_small(const GemmP& p, int groups, bool glu, bool pdl, cudaStream_t st) {
+    const dim3 grid(cdiv(glu ? p.N / 2 : p.N, kSmCols), groups), block(256);
+    const size_t smem = (size_t)8 * p.K * sizeof(T);
+    cudaError_t e = cudaSuccess;
+    static size_t set_glu = 0, set_plain = 0;
+    size_t& set_for = glu ? set_glu : set_plain;
+    if (smem > 48 * 1024 && smem > set_for) {
+        e = glu ? cudaFuncSetAttribute(k_gemm_grouped_small<T, TO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                : cudaFuncSetAttribute(k_gemm_grouped_small<T, TO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        set_for = smem;
+    }
+    return glu ? launch(k_gemm_grouped_small<T, TO, true>, grid, block, smem, st, pdl, p)
+               : launch(k_gemm_grouped_small<T, TO, false>, grid, block, smem, st, pdl, p);
+}
+
 // ---- fp32 inputs ---------------------------------------------------------------------------------------------------
 constexpr int kFK = 16;
 
@@ -387,6 +480,16 @@ static bool aligned_for(const void* ptr, long long ld, long long bstride, int K,
 
 using namespace zl;
 
+// row count of a step up to which grouped problems take the few-rows kernel (ZL_GEMM_GROUPED_SMALL_MAX overrides)
+static int grouped_small_max() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("ZL_GEMM_GROUPED_SMALL_MAX");
+        v = e ? atoi(e) : 32;
+    }
+    return v;
+}
+
 static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int epilogue, int pdl, cudaStream_t stream) {
     const int M = p.M, N = p.N, K = p.K;
     const bool grouped = p.grp_off != nullptr, pairs = epilogue == ZL_GEMM_EPI_GLU_CLAMP;
@@ -415,6 +518,14 @@ static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int ep
             e = launch(k_gemm_f32<ZL_GEMM_EPI_GLU_CLAMP>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
         else
             e = launch(k_gemm_f32<ZL_GEMM_EPI_NONE>, grid, block, 0, stream, pdl != 0, p, (int)vx, (int)vw);
+    } else if (grouped && M <= grouped_small_max() && vx && vw && K % 8 == 0 && (size_t)8 * K * 2 <= 160 * 1024 &&
+               (epilogue == ZL_GEMM_EPI_NONE || pairs)) {   // a decode step's experts: a handful of rows per group
+        if (in_dtype == ZL_BF16)
+            e = out_dtype == ZL_F32 ? launch_grouped_small<__nv_bfloat16, float>(p, batch, pairs, pdl != 0, stream)
+                                    : launch_grouped_small<__nv_bfloat16, __nv_bfloat16>(p, batch, pairs, pdl != 0, stream);
+        else
+            e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, batch, pairs, pdl != 0, stream)
+                                    : launch_grouped_small<__half, __half>(p, batch, pairs, pdl != 0, stream);
     } else if (!grouped && !pairs && M <= 8 && vx && vw && (size_t)M * K * 2 <= 48 * 1024) {   // few rows: stream the weights once per column
         if (in_dtype == ZL_BF16)
             e = out_dtype == ZL_F32 ? launch_small_m<__nv_bfloat16, float>(p, batch, epilogue, pdl != 0, stream)

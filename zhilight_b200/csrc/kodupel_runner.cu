@@ -331,7 +331,7 @@ int linear(zl_kodupel* m, const void* x, int K, const void* w, int N, const floa
     return zl_gemm_nt_bias(x, K, w, K, bias_f32, y, N, M, N, K, c.dtype, out_dtype, epi, 0, m->stream);
 }
 
-int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_len) {
+int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_run, int max_len) {
     const auto& c = m->cfg;
     const int D = c.width, dt = c.dtype;
     cudaStream_t st = m->stream;
@@ -359,7 +359,7 @@ int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_len) {
             const int splits = zl_sink_attention_splits(T, H, lc.kv_heads, max_len);
             RCHECK(zl_sink_attention(m->q, L.k_addrs, L.v_addrs, m->d_slots, m->d_pos, nullptr, m->proj + L.g_off, L.n_in,
                                      lc.scale, m->att, T, H, lc.kv_heads, lc.dim, lc.vdim, splits, m->attn_ws, m->attn_ws_bytes,
-                                     dt, 0, st));
+                                     m->d_run0, m->d_runlen, n_runs, max_run, dt, 0, st));
             RCHECK(linear(m, m->att, H * lc.vdim, L.o, D, L.o_b, L.o_b_act, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
         } else {
             const int hd = H * lc.dim;
@@ -398,15 +398,16 @@ int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_len) {
 }
 
 // decode-sized steps replay a CUDA graph per (rows, wanted rows, runs, length bucket); prompt portions are enqueued directly
-int run_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_len) {
+// (max_run: the longest run; a captured step is sized for the longest run its row count allows)
+int run_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_run, int max_len) {
     const int bucket = len_bucket(m, max_len);
-    if (!m->cfg.use_graph || T > m->cfg.max_batch || m->capture) return enqueue_step(m, T, n_want, n_runs, bucket);
+    if (!m->cfg.use_graph || T > m->cfg.max_batch || m->capture) return enqueue_step(m, T, n_want, n_runs, max_run, bucket);
     const long long key = ((long long)T << 48) | ((long long)n_want << 32) | ((long long)n_runs << 16) | (long long)(bucket >> 8);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         cudaGraph_t graph = nullptr;
         ZL_CHECK_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-        const int rc = enqueue_step(m, T, n_want, n_runs, bucket);
+        const int rc = enqueue_step(m, T, n_want, n_runs, T - n_runs + 1, bucket);
         const cudaError_t ce = cudaStreamEndCapture(m->stream, &graph);
         if (rc != ZL_OK) {
             if (graph) cudaGraphDestroy(graph);
@@ -579,7 +580,7 @@ extern "C" int zl_kodupel_step(zl_kodupel_t* m, const int32_t* tokens_host, cons
     ZL_CHECK_ARG(T <= m->tcap && n_want <= T && (n_want == 0 || want_rows_host));
     const auto& c = m->cfg;
     int32_t* hs = m->h_stage;
-    int max_len = 0, n_runs = 0;
+    int max_len = 0, n_runs = 0, max_run = 1;
     for (int i = 0; i < T; ++i) {
         ZL_CHECK_ARG(tokens_host[i] >= 0 && tokens_host[i] < c.vocab);
         ZL_CHECK_ARG(slots_host[i] >= 0 && slots_host[i] < c.max_batch);
@@ -588,6 +589,7 @@ extern "C" int zl_kodupel_step(zl_kodupel_t* m, const int32_t* tokens_host, cons
         if (i > 0 && slots_host[i] == slots_host[i - 1]) {
             ZL_CHECK_ARG(positions_host[i] == positions_host[i - 1] + 1);
             hs[6 * T + n_runs - 1] += 1;
+            if (hs[6 * T + n_runs - 1] > max_run) max_run = hs[6 * T + n_runs - 1];
         } else {
             hs[5 * T + n_runs] = i;
             hs[6 * T + n_runs] = 1;
@@ -609,7 +611,7 @@ extern "C" int zl_kodupel_step(zl_kodupel_t* m, const int32_t* tokens_host, cons
     ZL_CHECK_CUDA(cudaMemcpyAsync(m->d_run0, hs + 5 * T, (size_t)n_runs * 4, cudaMemcpyHostToDevice, st));
     ZL_CHECK_CUDA(cudaMemcpyAsync(m->d_runlen, hs + 6 * T, (size_t)n_runs * 4, cudaMemcpyHostToDevice, st));
     if (n_want) ZL_CHECK_CUDA(cudaMemcpyAsync(m->d_want, hs + 3 * T, (size_t)n_want * 4, cudaMemcpyHostToDevice, st));
-    RCHECK(run_step(m, T, n_want, n_runs, max_len));
+    RCHECK(run_step(m, T, n_want, n_runs, max_run, max_len));
     if (n_want && next_host) ZL_CHECK_CUDA(cudaMemcpyAsync(hs + 4 * T, m->d_next, (size_t)n_want * 4, cudaMemcpyDeviceToHost, st));
     if (n_want && logits_host)
         ZL_CHECK_CUDA(cudaMemcpyAsync(logits_host, m->logits, (size_t)n_want * c.vocab * 4, cudaMemcpyDeviceToHost, st));
@@ -649,7 +651,7 @@ extern "C" int zl_kodupel_set_state(zl_kodupel_t* m, const int32_t* tokens_host,
 extern "C" int zl_kodupel_step_device(zl_kodupel_t* m, int B) {
     ZL_CHECK_ARG(m && B > 0 && B <= m->cfg.max_batch);
     if (m->cur_max_len >= m->cfg.max_seq) return fail(__LINE__, "caches full (max_seq reached)");
-    RCHECK(run_step(m, B, B, B, m->cur_max_len));
+    RCHECK(run_step(m, B, B, B, 1, m->cur_max_len));
     k_decode_advance<<<cdiv(B, 64), 64, 0, m->stream>>>(m->d_tokens, m->d_pos, m->d_next, B);
     ZL_CHECK_LAUNCH();
     m->cur_max_len += 1;

@@ -105,18 +105,37 @@ template <typename TO>
 __global__ void __launch_bounds__(256) k_rmsnorm_residual_combine(const float* __restrict__ parts, long long ldp,
                                                                   const float* __restrict__ coef, int n_parts,
                                                                   const float* __restrict__ w, float* __restrict__ x,
-                                                                  long long ldx, TO* __restrict__ x_act, int D, float eps) {
+                                                                  long long ldx, TO* __restrict__ x_act, int D, float eps,
+                                                                  int vec) {
     __shared__ float red[8];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     const float* pr = parts + (size_t)t * n_parts * ldp;
     const float* cf = coef ? coef + (size_t)t * n_parts : nullptr;
+    // vec: D % 4 == 0, D <= 4096, 16-byte aligned rows: every thread keeps its (up to four) 4-channel sums in registers
+    float4 keep[4];
     float ss = 0.f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float s = 0.f;
-        for (int q = 0; q < n_parts; ++q) s = fmaf(cf ? cf[q] : 1.0f, pr[(size_t)q * ldp + c], s);
-        ss = fmaf(s, s, ss);
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c4 = threadIdx.x + i * 256;
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c4 * 4 < D)
+                for (int q = 0; q < n_parts; ++q) {
+                    const float a = cf ? cf[q] : 1.0f;
+                    const float4 v = *reinterpret_cast<const float4*>(pr + (size_t)q * ldp + c4 * 4);
+                    s.x = fmaf(a, v.x, s.x), s.y = fmaf(a, v.y, s.y), s.z = fmaf(a, v.z, s.z), s.w = fmaf(a, v.w, s.w);
+                }
+            keep[i] = s;
+            ss = fmaf(s.x, s.x, fmaf(s.y, s.y, fmaf(s.z, s.z, fmaf(s.w, s.w, ss))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            float s = 0.f;
+            for (int q = 0; q < n_parts; ++q) s = fmaf(cf ? cf[q] : 1.0f, pr[(size_t)q * ldp + c], s);
+            ss = fmaf(s, s, ss);
+        }
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -124,6 +143,22 @@ __global__ void __launch_bounds__(256) k_rmsnorm_residual_combine(const float* _
     float tot = 0.f;
     for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
     const float r = 1.0f / sqrtf(tot / (float)D + eps);
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            if (c >= D) continue;
+            const float4 wv = *reinterpret_cast<const float4*>(w + c);
+            float4 xv = *reinterpret_cast<float4*>(x + (size_t)t * ldx + c);
+            xv.x += keep[i].x * r * wv.x, xv.y += keep[i].y * r * wv.y, xv.z += keep[i].z * r * wv.z, xv.w += keep[i].w * r * wv.w;
+            *reinterpret_cast<float4*>(x + (size_t)t * ldx + c) = xv;
+            if (x_act) {
+                x_act[(size_t)t * D + c] = from_f32<TO>(xv.x), x_act[(size_t)t * D + c + 1] = from_f32<TO>(xv.y);
+                x_act[(size_t)t * D + c + 2] = from_f32<TO>(xv.z), x_act[(size_t)t * D + c + 3] = from_f32<TO>(xv.w);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float s = 0.f;
         for (int q = 0; q < n_parts; ++q) s = fmaf(cf ? cf[q] : 1.0f, pr[(size_t)q * ldp + c], s);
@@ -184,12 +219,14 @@ extern "C" int zl_rmsnorm_residual_combine(const float* parts, long long ldp, co
     ZL_CHECK_ARG(parts && weight && x && n_parts > 0 && T > 0 && D > 0 && ldp >= D && ldx >= D);
     ZL_CHECK_ARG(!x_act || act_dtype == ZL_F16 || act_dtype == ZL_BF16);
     cudaError_t e;
+    const int vec = D % 4 == 0 && D <= 4096 && ldp % 4 == 0 && ldx % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(parts) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
     if (x_act && act_dtype == ZL_F16)
         e = launch(k_rmsnorm_residual_combine<__half>, dim3(T), dim3(256), 0, stream, pdl != 0, parts, ldp, coef, n_parts, weight,
-                   x, ldx, (__half*)x_act, D, eps);
+                   x, ldx, (__half*)x_act, D, eps, vec);
     else
         e = launch(k_rmsnorm_residual_combine<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, pdl != 0, parts, ldp, coef, n_parts,
-                   weight, x, ldx, (__nv_bfloat16*)x_act, D, eps);
+                   weight, x, ldx, (__nv_bfloat16*)x_act, D, eps, vec);
     ZL_CHECK_CUDA(e);
     return ZL_OK;
 }

@@ -9,8 +9,33 @@
 
 namespace zl {
 
-// grid (T), 128 threads; dynamic shared memory 2 * E floats
-__global__ void __launch_bounds__(128) k_moe_route(const float* __restrict__ x, long long ldx,
+constexpr int kRouteWarps = 16;
+
+// row . row with independent 16-byte loads in flight (both rows 16-byte aligned, D % 4 == 0), else element by element
+__device__ __forceinline__ float route_dot(const float* __restrict__ a, const float* __restrict__ b, int D, int lane, bool vec) {
+    float acc0 = 0.f, acc1 = 0.f;
+    if (vec) {
+        const float4* a4 = reinterpret_cast<const float4*>(a);
+        const float4* b4 = reinterpret_cast<const float4*>(b);
+        const int n4 = D >> 2;
+        int c = lane;
+        for (; c + 32 < n4; c += 64) {
+            const float4 x0 = a4[c], y0 = b4[c], x1 = a4[c + 32], y1 = b4[c + 32];
+            acc0 = fmaf(x0.x, y0.x, fmaf(x0.y, y0.y, fmaf(x0.z, y0.z, fmaf(x0.w, y0.w, acc0))));
+            acc1 = fmaf(x1.x, y1.x, fmaf(x1.y, y1.y, fmaf(x1.z, y1.z, fmaf(x1.w, y1.w, acc1))));
+        }
+        for (; c < n4; c += 32) {
+            const float4 x0 = a4[c], y0 = b4[c];
+            acc0 = fmaf(x0.x, y0.x, fmaf(x0.y, y0.y, fmaf(x0.z, y0.z, fmaf(x0.w, y0.w, acc0))));
+        }
+    } else {
+        for (int c = lane; c < D; c += 32) acc0 = fmaf(a[c], b[c], acc0);
+    }
+    return warp_sum(acc0 + acc1);
+}
+
+// grid (T), 16 warps; dynamic shared memory 2 * E floats
+__global__ void __launch_bounds__(kRouteWarps * 32) k_moe_route(const float* __restrict__ x, long long ldx,
                                                    const float* __restrict__ w_router, const float* __restrict__ correction,
                                                    int32_t* __restrict__ top_e, float* __restrict__ top_w, int D, int E,
                                                    int top, int score_fn, int renorm) {
@@ -21,11 +46,9 @@ __global__ void __launch_bounds__(128) k_moe_route(const float* __restrict__ x, 
     pdl_wait();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float* xr = x + (size_t)t * ldx;
-    for (int e = warp; e < E; e += 4) {
-        const float* wr = w_router + (size_t)e * D;
-        float acc = 0.f;
-        for (int c = lane; c < D; c += 32) acc = fmaf(xr[c], wr[c], acc);
-        acc = warp_sum(acc);
+    const bool vec = (D & 3) == 0 && (ldx & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_router)) & 15) == 0;
+    for (int e = warp; e < E; e += kRouteWarps) {
+        const float acc = route_dot(xr, w_router + (size_t)e * D, D, lane, vec);
         if (lane == 0) score[e] = acc;
     }
     __syncthreads();
@@ -111,7 +134,7 @@ extern "C" int zl_moe_route(const float* x, long long ldx, const float* w_router
     ZL_CHECK_ARG(x && w_router && top_experts && top_weights && group_offsets && list_token && list_pair);
     ZL_CHECK_ARG(T > 0 && D > 0 && experts > 0 && top > 0 && top <= experts && experts <= 4096);
     ZL_CHECK_ARG(score_fn == ZL_MOE_SCORE_SIGMOID || score_fn == ZL_MOE_SCORE_SOFTMAX);
-    ZL_CHECK_CUDA(launch(k_moe_route, dim3(T), dim3(128), (size_t)2 * experts * sizeof(float), stream, pdl != 0, x, ldx, w_router,
+    ZL_CHECK_CUDA(launch(k_moe_route, dim3(T), dim3(kRouteWarps * 32), (size_t)2 * experts * sizeof(float), stream, pdl != 0, x, ldx, w_router,
                          correction, top_experts, top_weights, D, experts, top, score_fn, renormalize));
     ZL_CHECK_CUDA(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)2 * (experts + 1) * sizeof(int), stream, pdl != 0,
                          (const int32_t*)top_experts, T * top, experts, top, group_offsets, list_token, list_pair));

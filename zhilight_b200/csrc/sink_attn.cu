@@ -3,10 +3,20 @@
 // the output.  Token t of the step sees rows 0 .. pos[t] of the caches of slot[t]; the step's own keys and values are
 // appended before this runs, so prompts, portions of prompts and single decode tokens are the same case.
 //
+// k_sink_attn_mma (16-bit caches, head sizes that are multiples of 16, values up to 128 wide, at most 16 query heads per
+// key/value head): a CTA owns up to 64 rows = (consecutive tokens of one run) x (the query heads of one key/value
+// head), so prompts fill the tile with tokens and decode steps with the heads that share the cached bytes.  Keys and
+// values come in tiles of 64 rows (cp.async, double buffered); S = Q K^T and O += P V on mma.sync.m16n8k16 with fp32
+// accumulators, the scores' scale, mask and online softmax in fp32 registers.  The probabilities enter the second
+// product as a bfloat16 pair hi + lo (two MMAs), so that no weight is rounded to 8 bits.  The sink is the initial
+// (max, sum) = (sink, 1) of every row; with key splits it is added by the merge kernel instead.
 // k_sink_attn: any head sizes up to 256 and any dtype; scores, softmax and the weighted sum in fp32 FMAs.  One CTA per
 // (token, query head); its 8 warps take the keys j = warp, warp + 8, ... (a fixed assignment: the result of a token
 // does not depend on the step it is computed in) with an online softmax each, merged in warp order with the sink term.
 #include "common.cuh"
+
+#include <cstdlib>
+#include <type_traits>
 
 namespace zl {
 
@@ -106,6 +116,265 @@ __global__ void __launch_bounds__(kSaWarps * 32) k_sink_attn(SinkAttnP p) {
     }
 }
 
+// ---- tensor-core kernel ----------------------------------------------------------------------------------------------
+struct SinkAttnMmaP {
+    SinkAttnP a;
+    const int32_t *run_row0, *run_len;
+};
+
+constexpr int kTq = 64, kTk = 64;
+
+__device__ __forceinline__ void sa_cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void sa_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void sa_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void sa_ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ void sa_ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+template <typename T>
+__device__ __forceinline__ void sa_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void sa_mma<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    mma_16816_f16(d, a, b0, b1, d);
+}
+template <>
+__device__ __forceinline__ void sa_mma<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    mma_16816_bf16(d, a, b0, b1, d);
+}
+template <typename T>
+__device__ __forceinline__ uint32_t sa_pack(float x, float y) {
+    T a = from_f32<T>(x), b = from_f32<T>(y);
+    return (uint32_t) * reinterpret_cast<uint16_t*>(&a) | ((uint32_t) * reinterpret_cast<uint16_t*>(&b) << 16);
+}
+
+// grid (ceil(longest run / tokens per tile), G, runs * splits); 4 warps of 16 rows.  NV: 8-column value tiles per warp.
+template <typename T, int NV>
+__global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
+    extern __shared__ __align__(16) unsigned char sa_raw[];
+    const SinkAttnP& p = pp.a;
+    const int DP = p.d + 8, VP = NV * 8 + 8;
+    T* sQ = reinterpret_cast<T*>(sa_raw);   // [kTq][DP]
+    T* sK = sQ + kTq * DP;                  // [2][kTk][DP]
+    T* sV = sK + 2 * kTk * DP;              // [2][kTk][VP]
+    pdl_trigger();
+    pdl_wait();
+    const int run = blockIdx.z / p.splits, split = blockIdx.z % p.splits, g = blockIdx.y;
+    const int R = p.H / p.G, nq = kTq / R;
+    const int len = pp.run_len[run], t0 = blockIdx.x * nq;
+    if (t0 >= len) return;
+    const int ntok = min(nq, len - t0), row0 = pp.run_row0[run] + t0;
+    const int sl = p.slot[row0], pos0 = p.pos[row0];
+    const int n_keys = pos0 + ntok;
+    int k_lo = 0, k_hi = n_keys;
+    if (p.splits > 1) {
+        const int per = cdiv(cdiv(n_keys, p.splits), kTk) * kTk;
+        k_lo = split * per;
+        k_hi = min(n_keys, k_lo + per);
+    }
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+    const int d8 = p.d >> 3, v8 = p.vd >> 3;
+    const T* kc = static_cast<const T*>(p.k_addrs[sl]) + (size_t)g * p.d;
+    const T* vc = static_cast<const T*>(p.v_addrs[sl]) + (size_t)g * p.vd;
+    const size_t kst = (size_t)p.G * p.d, vst = (size_t)p.G * p.vd;
+
+    auto load_kv = [&](int buf, int k0) {
+        T* dk = sK + (size_t)buf * kTk * DP;
+        T* dv = sV + (size_t)buf * kTk * VP;
+        for (int i = tid; i < kTk * d8; i += 128) {
+            const int r = i / d8, c = i - r * d8, kj = k0 + r;
+            if (kj < k_hi) sa_cp_async16(dk + (size_t)r * DP + c * 8, kc + (size_t)kj * kst + c * 8);
+            else *reinterpret_cast<uint4*>(dk + (size_t)r * DP + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+        for (int i = tid; i < kTk * (NV + 0); i += 128) {
+            const int r = i / NV, c = i - r * NV, kj = k0 + r;
+            if (kj < k_hi && c < v8) sa_cp_async16(dv + (size_t)r * VP + c * 8, vc + (size_t)kj * vst + c * 8);
+            else *reinterpret_cast<uint4*>(dv + (size_t)r * VP + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+    };
+    // rows of this thread: warp * 16 + gq and + 8; row -> (token, head in the group)
+    int tok_of[2], pos_of[2], head_of[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int r = warp * 16 + gq + hh * 8;
+        tok_of[hh] = r / R;
+        head_of[hh] = g * R + (r - tok_of[hh] * R);
+        row_ok[hh] = tok_of[hh] < ntok;
+        pos_of[hh] = pos0 + tok_of[hh];
+    }
+    float m_run[2], l_run[2], O[NV][4];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const float sink = p.sink ? p.sink[head_of[hh] < p.H ? head_of[hh] : 0] : 0.f;
+        m_run[hh] = p.splits > 1 ? -1e30f : sink;
+        l_run[hh] = (p.splits > 1 || tq != 0) ? 0.f : 1.f;   // the sink's exp(sink - m) = 1, held by one thread of the quad
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) O[j][c] = 0.f;
+
+    if (k_lo < k_hi) {
+        // the query tile
+        for (int i = tid; i < kTq * d8; i += 128) {
+            const int r = i / d8, c = i - r * d8, tk = r / R;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (tk < ntok)
+                v = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + ((size_t)(row0 + tk) * p.H + g * R + (r - tk * R)) * p.d + c * 8);
+            *reinterpret_cast<uint4*>(sQ + (size_t)r * DP + c * 8) = v;
+        }
+        load_kv(0, k_lo);
+        sa_cp_commit();
+        int buf = 0;
+        for (int k0 = k_lo; k0 < k_hi; k0 += kTk, buf ^= 1) {
+            sa_cp_wait<0>();
+            __syncthreads();   // tile k0 (and the query tile) is in shared memory; every warp is done with the other buffer
+            if (k0 + kTk < k_hi) load_kv(buf ^ 1, k0 + kTk);
+            sa_cp_commit();
+            const T* tK = sK + (size_t)buf * kTk * DP;
+            const T* tV = sV + (size_t)buf * kTk * VP;
+            float S[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) S[j][c] = 0.f;
+            for (int kk = 0; kk < p.d; kk += 16) {
+                uint32_t a[4];
+                sa_ldmatrix_x4(a, sQ + (size_t)(warp * 16 + (lane & 15)) * DP + kk + (lane >> 4) * 8);
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    uint32_t b[4];
+                    sa_ldmatrix_x4(b, tK + (size_t)(jj * 16 + (lane & 7) + (lane >> 4) * 8) * DP + kk + ((lane >> 3) & 1) * 8);
+                    sa_mma<T>(S[2 * jj], a, b[0], b[1]);
+                    sa_mma<T>(S[2 * jj + 1], a, b[2], b[3]);
+                }
+            }
+            // scale, mask, online softmax (rows gq and gq + 8 of the warp's 16)
+            float mx[2] = {-1e30f, -1e30f};
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int hh = c >> 1, key = k0 + 8 * j + 2 * tq + (c & 1);
+                    const bool ok = row_ok[hh] && key < k_hi && key <= pos_of[hh];
+                    S[j][c] = ok ? S[j][c] * p.scale : -1e30f;
+                    mx[hh] = fmaxf(mx[hh], S[j][c]);
+                }
+            float corr[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+                mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+                const float mn = fmaxf(m_run[hh], mx[hh]);
+                corr[hh] = expf(m_run[hh] - mn);
+                m_run[hh] = mn;
+                l_run[hh] *= corr[hh];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int hh = c >> 1;
+                    const float pr = S[j][c] > -1e29f ? expf(S[j][c] - m_run[hh]) : 0.f;
+                    S[j][c] = pr;
+                    l_run[hh] += pr;
+                }
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                O[j][0] *= corr[0], O[j][1] *= corr[0];
+                O[j][2] *= corr[1], O[j][3] *= corr[1];
+            }
+            // O += P V, 16 keys at a time
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2) {
+                uint32_t ah[4], al[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float x = S[2 * k2 + (r >> 1)][(r & 1) * 2], y = S[2 * k2 + (r >> 1)][(r & 1) * 2 + 1];
+                    ah[r] = sa_pack<T>(x, y);
+                    if constexpr (sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+                        const float xh = round_to<T>(x), yh = round_to<T>(y);
+                        al[r] = sa_pack<T>(x - xh, y - yh);
+                    }
+                }
+#pragma unroll
+                for (int nn = 0; nn < NV / 2; ++nn) {
+                    uint32_t b[4];
+                    sa_ldmatrix_x4_trans(b, tV + (size_t)(k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + nn * 16 + (lane >> 4) * 8);
+                    sa_mma<T>(O[2 * nn], ah, b[0], b[1]);
+                    sa_mma<T>(O[2 * nn + 1], ah, b[2], b[3]);
+                    if constexpr (!std::is_same<T, __half>::value) {
+                        sa_mma<T>(O[2 * nn], al, b[0], b[1]);
+                        sa_mma<T>(O[2 * nn + 1], al, b[2], b[3]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        if (!row_ok[hh]) continue;
+        const int t = row0 + tok_of[hh], h = head_of[hh];
+        if (p.splits > 1) {
+            float* part = p.ws + (((size_t)t * p.H + h) * p.splits + split) * (2 + p.vd);
+            const bool empty = l_run[hh] <= 0.f;
+            if (tq == 0) part[0] = empty ? -INFINITY : m_run[hh], part[1] = empty ? 0.f : l_run[hh];
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int c = 8 * j + 2 * tq;
+                if (c < p.vd) part[2 + c] = O[j][hh * 2], part[2 + c + 1] = O[j][hh * 2 + 1];
+            }
+        } else {
+            float gate = 1.0f;
+            if (p.gate) gate = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.ldg + h]));
+            const float inv = gate / l_run[hh];
+            T* out = static_cast<T*>(p.out) + ((size_t)t * p.H + h) * p.vd;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int c = 8 * j + 2 * tq;
+                if (c < p.vd) {
+                    out[c] = from_f32<T>(O[j][hh * 2] * inv);
+                    out[c + 1] = from_f32<T>(O[j][hh * 2 + 1] * inv);
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int NV>
+static cudaError_t launch_sink_mma(const SinkAttnMmaP& pp, int runs, int max_run_len, bool pdl, cudaStream_t st) {
+    const SinkAttnP& p = pp.a;
+    const int nq = kTq / (p.H / p.G);
+    const size_t smem = ((size_t)kTq * (p.d + 8) + 2 * (size_t)kTk * (p.d + 8) + 2 * (size_t)kTk * (NV * 8 + 8)) * sizeof(T);
+    static size_t set_for = 0;
+    if (smem > 48 * 1024 && smem > set_for) {
+        const cudaError_t e = cudaFuncSetAttribute(k_sink_attn_mma<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        set_for = smem;
+    }
+    return launch(k_sink_attn_mma<T, NV>, dim3(cdiv(max_run_len, nq), p.G, runs * p.splits), dim3(128), smem, st, pdl, pp);
+}
+template <typename T>
+static cudaError_t launch_sink_mma_t(const SinkAttnMmaP& pp, int runs, int max_run_len, bool pdl, cudaStream_t st) {
+    if (pp.a.vd <= 32) return launch_sink_mma<T, 4>(pp, runs, max_run_len, pdl, st);
+    if (pp.a.vd <= 64) return launch_sink_mma<T, 8>(pp, runs, max_run_len, pdl, st);
+    return launch_sink_mma<T, 16>(pp, runs, max_run_len, pdl, st);
+}
+
 // merge of the splits with the sink term and the gate; one warp per (token, head), grid (ceil(H / 4), T)
 template <typename T>
 __global__ void __launch_bounds__(128) k_sink_attn_merge(SinkAttnP p) {
@@ -156,7 +425,8 @@ extern "C" int zl_sink_attention_splits(int T, int heads, int kv_heads, int max_
 extern "C" int zl_sink_attention(const void* q, void* const* k_addrs, void* const* v_addrs, const int32_t* slot,
                                  const int32_t* pos, const float* sink, const float* gate, long long ldg, float scale, void* out,
                                  int T, int heads, int kv_heads, int dim, int vdim, int splits, void* workspace,
-                                 size_t workspace_bytes, int dtype, int pdl, zl_stream_t stream) {
+                                 size_t workspace_bytes, const int32_t* run_row0, const int32_t* run_len, int runs,
+                                 int max_run_len, int dtype, int pdl, zl_stream_t stream) {
     ZL_CHECK_ARG(q && k_addrs && v_addrs && slot && pos && out && T > 0 && T <= 65535 && heads > 0 && kv_heads > 0);
     ZL_CHECK_ARG(heads % kv_heads == 0 && dim > 0 && vdim > 0);
     ZL_CHECK_SUPPORTED(vdim <= 32 * kSaMaxPerLane);
@@ -168,7 +438,15 @@ extern "C" int zl_sink_attention(const void* q, void* const* k_addrs, void* cons
     const dim3 grid(heads, T, splits), block(kSaWarps * 32);
     const size_t smem = ((size_t)dim + 2 * kSaWarps + (size_t)kSaWarps * vdim) * sizeof(float);
     cudaError_t e;
-    if (dtype == ZL_F32) e = launch(k_sink_attn<float>, grid, block, smem, stream, pdl != 0, p);
+    static const bool no_mma = getenv("ZL_SINK_ATTN_NO_MMA") != nullptr;
+    const bool mma = !no_mma && run_row0 && run_len && runs > 0 && max_run_len > 0 && dtype != ZL_F32 && dim % 16 == 0 &&
+                     vdim % 8 == 0 && vdim <= 128 && dim <= 256 && heads / kv_heads <= 16 && kTq % (heads / kv_heads) == 0;
+    if (mma) {
+        ZL_CHECK_ARG((long long)runs * splits <= 65535 && kv_heads <= 65535);
+        SinkAttnMmaP pp{p, run_row0, run_len};
+        e = dtype == ZL_BF16 ? launch_sink_mma_t<__nv_bfloat16>(pp, runs, max_run_len, pdl != 0, stream)
+                             : launch_sink_mma_t<__half>(pp, runs, max_run_len, pdl != 0, stream);
+    } else if (dtype == ZL_F32) e = launch(k_sink_attn<float>, grid, block, smem, stream, pdl != 0, p);
     else if (dtype == ZL_BF16) e = launch(k_sink_attn<__nv_bfloat16>, grid, block, smem, stream, pdl != 0, p);
     else e = launch(k_sink_attn<__half>, grid, block, smem, stream, pdl != 0, p);
     ZL_CHECK_CUDA(e);

@@ -475,3 +475,113 @@ def group_norm_conv(x, norm_weight, taps_weight, slot, pos, ring, groups, eps, o
     _lib.call("zl_group_norm_conv", _p(x), d, _p(norm_weight), _p(taps_weight), _p(slot), _p(pos), _p(ring), _p(h), _p(u), t, d,
               groups, taps_weight.shape[1], eps, _dt(u), 0, _stream())
     return h, u
+
+
+# ------------------------------------------------------------------ per-head norms, rotation, sink attention, delta rule, experts
+GEMM_EPI_TANH, GEMM_EPI_GLU_CLAMP = 3, 4
+MOE_SCORE_SIGMOID, MOE_SCORE_SOFTMAX = 0, 1
+
+
+def gemm_nt_bias(x, w, bias=None, out_dtype=None, epilogue=GEMM_EPI_NONE):
+    """y = epi(x @ w^T + bias); x (M, K), w (N, K), bias (N) fp32 or None; epilogue none, relu^2 or tanh."""
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype or x.dtype, device=x.device)
+    _lib.call("zl_gemm_nt_bias", _p(x), k, _p(w), k, _p(bias), _p(y), n, m, n, k, _dt(x), _dt(y), epilogue, 0, _stream())
+    return y
+
+
+def gemm_nt_grouped(x, w, group_offsets, rows_out, x_rows=None, y_rows=None, out_dtype=None, epilogue=GEMM_EPI_NONE, limit=0.0,
+                    alpha=1.0, beta=0.0):
+    """Grouped y = epi(x[x_rows] @ w[g]^T) scattered to y[y_rows]; w (G, N, K); group_offsets (G + 1) int32 over a list
+    sorted by group; y has `rows_out` rows of N (N / 2 with the gated-unit epilogue) columns, zero where nothing lands."""
+    g, n, k = w.shape
+    n_out = n // 2 if epilogue == GEMM_EPI_GLU_CLAMP else n
+    y = torch.zeros((rows_out, n_out), dtype=out_dtype or x.dtype, device=x.device)
+    total = (x_rows if x_rows is not None else y_rows if y_rows is not None else x).shape[0]
+    _lib.call("zl_gemm_nt_grouped", _p(x), x.shape[1], _p(x_rows), _p(w), k, n * k, _p(y), n_out, _p(y_rows), _p(group_offsets),
+              g, total, n, k, _dt(x), _dt(y), epilogue, limit, alpha, beta, 0, _stream())
+    return y
+
+
+def rope_inv_freq_yarn(base, dims, factor=0.0, original=0.0, fast=0.0, slow=0.0):
+    """-> (frequencies (dims / 2) float32 numpy array, cos / sin scale)."""
+    import numpy as np
+    out = np.zeros(max(dims // 2, 1), dtype=np.float32)
+    ms = ctypes.c_float()
+    _lib.call("zl_rope_inv_freq_yarn", float(base), dims, float(factor), float(original), float(fast), float(slow),
+              out.ctypes.data_as(ctypes.c_void_p), ctypes.cast(ctypes.byref(ms), ctypes.c_void_p))
+    return out[:dims // 2], ms.value
+
+
+def qkv_headnorm_rope_append(proj, q_off, k_off, v_off, heads, kv_heads, dim, vdim, q_weight, k_weight, inv_freq, rot_dims,
+                             mscale, eps, k_cache, v_cache, k_table, v_table, slot, pos, dtype):
+    """proj (T, ld) fp32 -> q (T, heads * dim) of `dtype`; keys / values go to rows (slot, pos) of the caches
+    (slots, rows, kv_heads * dim) / (slots, rows, kv_heads * vdim) unless k_off < 0."""
+    t, ldp = proj.shape
+    q = torch.empty((t, heads * dim), dtype=dtype, device=proj.device)
+    _lib.call("zl_qkv_headnorm_rope_append", _p(proj), ldp, q_off, k_off, v_off, heads, kv_heads, dim, vdim, _p(q_weight),
+              _p(k_weight), _p(inv_freq), rot_dims, mscale, eps, _p(q), _p(k_table), _p(v_table), _p(slot), _p(pos), t, _dt(q),
+              0, _stream())
+    return q
+
+
+def sink_attention(q, k_table, v_table, slot, pos, scale, heads, kv_heads, dim, vdim, sink=None, gate=None, splits=1,
+                   run_row0=None, run_len=None, max_run_len=0):
+    """q (T, heads * dim) -> (T, heads * vdim); gate (T, ld) fp32 logits whose first `heads` columns gate the heads.
+    run_row0 / run_len (int32 device tensors) describe the step's runs and select the tensor-core kernel."""
+    t = q.shape[0]
+    lib = _lib.load()
+    nbytes = lib.zl_sink_attention_workspace_bytes(t, heads, vdim, splits)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    out = torch.empty((t, heads * vdim), dtype=q.dtype, device=q.device)
+    _lib.call("zl_sink_attention", _p(q), _p(k_table), _p(v_table), _p(slot), _p(pos), _p(sink), _p(gate),
+              gate.shape[1] if gate is not None else 0, scale, _p(out), t, heads, kv_heads, dim, vdim, splits, _p(ws), nbytes,
+              _p(run_row0), _p(run_len), run_row0.numel() if run_row0 is not None else 0, max_run_len, _dt(q), 0, _stream())
+    return out
+
+
+def head_rmsnorm_gate(o, heads, vdim, eps, weight=None, gate=None, out_dtype=torch.float32):
+    """o (T, heads * vdim) fp32: each head divided by its RMS, times weight (heads * vdim), times sigmoid(gate) (same shape)."""
+    t = o.shape[0]
+    y = torch.empty((t, heads * vdim), dtype=out_dtype, device=o.device)
+    _lib.call("zl_head_rmsnorm_gate", _p(o), heads * vdim, _p(weight), _p(gate), heads * vdim, _p(y), heads * vdim, t, heads,
+              vdim, eps, _dt(y), 0, _stream())
+    return y
+
+
+def rmsnorm_residual_combine(parts, coef, weight, x, eps, act_dtype=None):
+    """x (T, D) fp32 += weight * rmsnorm(sum_p coef[t, p] * parts[t, p]); parts (T, n_parts, D) fp32, coef (T, n_parts) or None.
+    Returns the new x rounded to act_dtype when that is given."""
+    t, n_parts, d = parts.shape
+    xa = torch.empty((t, d), dtype=act_dtype, device=x.device) if act_dtype is not None else None
+    _lib.call("zl_rmsnorm_residual_combine", _p(parts), d, _p(coef), n_parts, _p(weight), _p(x), d, _p(xa),
+              _dt(xa) if xa is not None else BF16, t, d, eps, 0, _stream())
+    return xa
+
+
+def delta_rule(r, k, v, rate_logit, decay_logit, decay_scale, unit_eps, run_row0, run_len, slot, pos, state, state_table, heads,
+               dim_k, dim_v):
+    """All inputs (T, heads * dim) fp32; state (slots, heads, dim_k, dim_v) fp32 is updated in place.  -> o (T, heads * dim_v)."""
+    t = r.shape[0]
+    o = torch.empty((t, heads * dim_v), dtype=torch.float32, device=r.device)
+    _lib.call("zl_delta_rule", _p(r), heads * dim_k, _p(k), heads * dim_k, _p(v), heads * dim_v, _p(rate_logit), heads * dim_k,
+              _p(decay_logit), heads * dim_k, decay_scale, unit_eps, _p(run_row0), _p(run_len), run_row0.numel(), _p(slot),
+              _p(pos), _p(state_table), _p(o), heads * dim_v, heads, dim_k, dim_v, 0, _stream())
+    return o
+
+
+def moe_route(x, w_router, correction, top, score_fn=MOE_SCORE_SIGMOID, renormalize=False):
+    """x (T, D) fp32, w_router (E, D) fp32 -> (experts (T, top) int32, weights (T, top) fp32, group offsets (E + 1),
+    list_token (T * top), list_pair (T * top))."""
+    t, d = x.shape
+    e = w_router.shape[0]
+    dev = x.device
+    te = torch.empty((t, top), dtype=torch.int32, device=dev)
+    tw = torch.empty((t, top), dtype=torch.float32, device=dev)
+    off = torch.empty(e + 1, dtype=torch.int32, device=dev)
+    lt = torch.empty(t * top, dtype=torch.int32, device=dev)
+    lp = torch.empty(t * top, dtype=torch.int32, device=dev)
+    _lib.call("zl_moe_route", _p(x), d, _p(w_router), _p(correction), _p(te), _p(tw), _p(off), _p(lt), _p(lp), t, d, e, top,
+              score_fn, int(renormalize), 0, _stream())
+    return te, tw, off, lt, lp
