@@ -555,13 +555,15 @@ int zl_rmsnorm_residual_combine(const float* parts, long long ldp, const float* 
 /* Generalized delta rule over the runs of a step (run i = rows run_row0[i] .. + run_len[i], one slot, consecutive
  * positions): per head a (dim_k, dim_v) fp32 state S in state_addrs[slot] ((heads, dim_k, dim_v)), zero at position 0,
  * S <- diag(w) S - (a * u)(u^T S) + k v^T, o = S^T r, with u = k / sqrt(sum(k^2) + unit_eps),
- * w = exp(-decay_scale * sigmoid(decay_logit)), a = sigmoid(rate_logit).  All inputs fp32 (T, heads * dim). */
+ * w = exp(-decay_scale * sigmoid(decay_logit)), a = sigmoid(rate_logit).  All inputs fp32 (T, heads * dim); T rows in
+ * the step; workspace of zl_delta_rule_workspace_bytes. */
 int zl_delta_rule_prepare(int dim_k, int dim_v);
+size_t zl_delta_rule_workspace_bytes(int T, int heads, int dim_k, int dim_v);
 int zl_delta_rule(const float* r, long long ld_r, const float* k, long long ld_k, const float* v, long long ld_v,
                   const float* rate_logit, long long ld_a, const float* decay_logit, long long ld_w, float decay_scale,
                   float unit_eps, const int32_t* run_row0, const int32_t* run_len, int runs, const int32_t* slot,
                   const int32_t* pos, void* const* state_addrs, float* o, long long ld_o, int heads, int dim_k, int dim_v,
-                  int pdl, zl_stream_t stream);
+                  int T, void* workspace, size_t workspace_bytes, int pdl, zl_stream_t stream);
 /* Routing of a mixture of experts: logits W_router x[t] (fp32), scores (sigmoid, or softmax over the experts), the
  * `top` largest of score + correction (NULL: none), weights = their scores (renormalize: divided by their sum) ->
  * top_experts / top_weights (T, top); and the (token, choice) pairs sorted by expert for zl_gemm_nt_grouped:

@@ -6,9 +6,9 @@
 // The columns of S (one per value channel) never meet: S_t[:, j] depends on S_(t-1)[:, j] and on the token's vectors
 // only.  A thread owns one column and walks the tokens of its sequence in order, so the result of a token does not
 // depend on how the sequence was cut into steps or on the other sequences of the step.  A CTA owns `cols` columns of
-// one head of one run (the consecutive rows of one slot in the step); the token vectors (u, a*u, w, k, r) of a chunk of
-// tokens are prepared by the whole CTA in shared memory, then every thread updates its column for the chunk without
-// any barrier.  The column lives in registers when dk is one of the compiled sizes, in shared memory otherwise.
+// one head of one run (the consecutive rows of one slot in the step).  The token vectors (u, a*u, w, k, r, v) are
+// prepared for all tokens at once by a kernel of their own; the recurrence stages them chunk by chunk in shared
+// memory ahead of use.  The column lives in registers when dk is one of the compiled sizes, in shared memory otherwise.
 // A run that starts at position 0 starts from a zero state (a slot given to a new sequence needs no clearing); the
 // final state goes back to the slot.  Everything is fp32.
 #include "common.cuh"
@@ -17,7 +17,7 @@
 
 namespace zl {
 
-constexpr int kDrChunk = 8;   // tokens prepared at a time
+constexpr int kDrChunk = 16;   // tokens staged at a time
 
 struct DeltaP {
     const float *r, *k, *v, *rate_logit, *decay_logit;   // (T, H * dk) / v: (T, H * dv), row strides below
@@ -29,25 +29,76 @@ struct DeltaP {
     long long ld_o;
     int H, dk, dv, cols;
     float decay_scale, unit_eps;
+    float* prep;                         // (T, H, 5 * dk + dv): u, a*u, w, k, r, v of every token and head
 };
 
+// The token vectors of the recurrence, for all tokens at once: one warp per (token, head).  grid (ceil(H / 4), T)
+__global__ void __launch_bounds__(128) k_delta_prep(DeltaP p) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.y, h = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (h >= p.H) return;
+    const int dk = p.dk;
+    const float* kr = p.k + (size_t)t * p.ld_k + (size_t)h * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss = fmaf(kr[i], kr[i], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) + p.unit_eps);
+    float* tv = p.prep + ((size_t)t * p.H + h) * (5 * dk + p.dv);
+    for (int i = lane; i < dk; i += 32) {
+        const float kk = kr[i], u = kk * inv;
+        const float a = 1.0f / (1.0f + expf(-p.rate_logit[(size_t)t * p.ld_a + (size_t)h * dk + i]));
+        const float sg_w = 1.0f / (1.0f + expf(-p.decay_logit[(size_t)t * p.ld_w + (size_t)h * dk + i]));
+        tv[i] = u;
+        tv[dk + i] = a * u;
+        tv[2 * dk + i] = expf(-p.decay_scale * sg_w);
+        tv[3 * dk + i] = kk;
+        tv[4 * dk + i] = p.r[(size_t)t * p.ld_r + (size_t)h * dk + i];
+    }
+    for (int j = lane; j < p.dv; j += 32) tv[5 * dk + j] = p.v[(size_t)t * p.ld_v + (size_t)h * p.dv + j];
+}
+
+__device__ __forceinline__ void dr_cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void dr_cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void dr_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void dr_cp_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // grid (dv / cols rounded up, H, runs); block = cols rounded up to a warp.  DK > 0: the column in registers.
+// The prepared vectors of the next chunk of tokens fly into the other half of the shared buffer (cp.async) while the
+// threads update their columns for the current chunk, so that no load sits on the chain from token to token.
 template <int DK>
 __global__ void k_delta_rule(DeltaP p) {
-    extern __shared__ float dsm[];
+    extern __shared__ __align__(16) float dsm[];
     const int dk = DK > 0 ? DK : p.dk;
-    float* tok = dsm;                                   // [kDrChunk][5][dk]: u, a*u, w, k, r
-    float* scol = dsm + (size_t)kDrChunk * 5 * dk;      // DK == 0: [dk][blockDim] the columns of this CTA
+    const int per = 5 * dk + p.dv;                      // floats per (token, head)
+    float* tok = dsm;                                   // [2][kDrChunk][per]
+    float* scol = dsm + (size_t)2 * kDrChunk * per;     // DK == 0: [dk][blockDim] the columns of this CTA
     pdl_trigger();
     pdl_wait();
     const int run = blockIdx.z, h = blockIdx.y, tid = threadIdx.x, nth = blockDim.x;
-    const int warp = tid >> 5, lane = tid & 31, nw = nth >> 5;
     const int row0 = p.run_row0[run], len = p.run_len[run];
     if (len <= 0) return;
     const int j = blockIdx.x * p.cols + tid;            // my value channel
     const bool mine = tid < p.cols && j < p.dv;
     float* sg = static_cast<float*>(p.state_addrs[p.slot[row0]]) + (size_t)h * dk * p.dv;
     const bool fresh = p.pos[row0] == 0;
+    const bool vec = (per & 3) == 0;
+    auto stage = [&](int buf, int c0) {
+        const int cn = min(kDrChunk, len - c0);
+        float* dst = tok + (size_t)buf * kDrChunk * per;
+        for (int tt = 0; tt < cn; ++tt) {
+            const float* src = p.prep + ((size_t)(row0 + c0 + tt) * p.H + h) * per;
+            if (vec)
+                for (int i = tid * 4; i < per; i += nth * 4) dr_cp_async16(dst + (size_t)tt * per + i, src + i);
+            else
+                for (int i = tid; i < per; i += nth) dr_cp_async4(dst + (size_t)tt * per + i, src + i);
+        }
+    };
+    stage(0, 0);
+    dr_cp_commit();
     float S[DK > 0 ? DK : 1];
     if (mine) {
         if constexpr (DK > 0) {
@@ -57,44 +108,43 @@ __global__ void k_delta_rule(DeltaP p) {
             for (int i = 0; i < dk; ++i) scol[(size_t)i * nth + tid] = fresh ? 0.f : sg[(size_t)i * p.dv + j];
         }
     }
-    for (int c0 = 0; c0 < len; c0 += kDrChunk) {
+    int buf = 0;
+    for (int c0 = 0; c0 < len; c0 += kDrChunk, buf ^= 1) {
         const int cn = min(kDrChunk, len - c0);
-        __syncthreads();   // the previous chunk's vectors are no longer read
-        for (int tt = warp; tt < cn; tt += nw) {
-            const size_t t = (size_t)(row0 + c0 + tt);
-            const float* kr = p.k + t * p.ld_k + (size_t)h * dk;
-            float ss = 0.f;
-            for (int i = lane; i < dk; i += 32) ss = fmaf(kr[i], kr[i], ss);
-            const float inv = 1.0f / sqrtf(warp_sum(ss) + p.unit_eps);
-            float* tv = tok + (size_t)tt * 5 * dk;
-            for (int i = lane; i < dk; i += 32) {
-                const float kk = kr[i], u = kk * inv;
-                const float a = 1.0f / (1.0f + expf(-p.rate_logit[t * p.ld_a + (size_t)h * dk + i]));
-                const float sg_w = 1.0f / (1.0f + expf(-p.decay_logit[t * p.ld_w + (size_t)h * dk + i]));
-                tv[i] = u;
-                tv[dk + i] = a * u;
-                tv[2 * dk + i] = expf(-p.decay_scale * sg_w);
-                tv[3 * dk + i] = kk;
-                tv[4 * dk + i] = p.r[t * p.ld_r + (size_t)h * dk + i];
-            }
-        }
-        __syncthreads();
+        dr_cp_wait_all();
+        __syncthreads();   // this chunk has landed for every thread; the other half is no longer read
+        if (c0 + kDrChunk < len) stage(buf ^ 1, c0 + kDrChunk);
+        dr_cp_commit();
         if (!mine) continue;
         for (int tt = 0; tt < cn; ++tt) {
             const size_t t = (size_t)(row0 + c0 + tt);
-            const float* tv = tok + (size_t)tt * 5 * dk;
-            const float vj = p.v[t * p.ld_v + (size_t)h * p.dv + j];
-            float dot = 0.f, out = 0.f;
+            const float* tv = tok + ((size_t)buf * kDrChunk + tt) * per;
+            const float vj = tv[5 * dk + blockIdx.x * p.cols + tid];
+            float out = 0.f;
             if constexpr (DK > 0) {
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;   // four chains; added in a fixed order
 #pragma unroll
-                for (int i = 0; i < DK; ++i) dot = fmaf(tv[i], S[i], dot);
-#pragma unroll
-                for (int i = 0; i < DK; ++i) {
-                    const float s = fmaf(tv[3 * DK + i], vj, fmaf(-tv[DK + i], dot, tv[2 * DK + i] * S[i]));
-                    S[i] = s;
-                    out = fmaf(s, tv[4 * DK + i], out);
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 u = *reinterpret_cast<const float4*>(tv + i);
+                    d0 = fmaf(u.x, S[i], d0), d1 = fmaf(u.y, S[i + 1], d1), d2 = fmaf(u.z, S[i + 2], d2), d3 = fmaf(u.w, S[i + 3], d3);
                 }
+                const float dot = (d0 + d1) + (d2 + d3);
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DK; i += 4) {
+                    const float4 au = *reinterpret_cast<const float4*>(tv + DK + i);
+                    const float4 w = *reinterpret_cast<const float4*>(tv + 2 * DK + i);
+                    const float4 kk = *reinterpret_cast<const float4*>(tv + 3 * DK + i);
+                    const float4 rr = *reinterpret_cast<const float4*>(tv + 4 * DK + i);
+                    S[i] = fmaf(kk.x, vj, fmaf(-au.x, dot, w.x * S[i]));
+                    S[i + 1] = fmaf(kk.y, vj, fmaf(-au.y, dot, w.y * S[i + 1]));
+                    S[i + 2] = fmaf(kk.z, vj, fmaf(-au.z, dot, w.z * S[i + 2]));
+                    S[i + 3] = fmaf(kk.w, vj, fmaf(-au.w, dot, w.w * S[i + 3]));
+                    o0 = fmaf(S[i], rr.x, o0), o1 = fmaf(S[i + 1], rr.y, o1), o2 = fmaf(S[i + 2], rr.z, o2), o3 = fmaf(S[i + 3], rr.w, o3);
+                }
+                out = (o0 + o1) + (o2 + o3);
             } else {
+                float dot = 0.f;
                 for (int i = 0; i < dk; ++i) dot = fmaf(tv[i], scol[(size_t)i * nth + tid], dot);
                 for (int i = 0; i < dk; ++i) {
                     const float s = fmaf(tv[3 * dk + i], vj, fmaf(-tv[dk + i], dot, tv[2 * dk + i] * scol[(size_t)i * nth + tid]));
@@ -115,10 +165,15 @@ __global__ void k_delta_rule(DeltaP p) {
     }
 }
 
+static size_t delta_smem(int DK, int dk, int dv, int block) {
+    size_t smem = (size_t)2 * kDrChunk * (5 * dk + dv) * sizeof(float);
+    if (DK == 0) smem += (size_t)dk * block * sizeof(float);
+    return smem;
+}
+
 template <int DK>
 static int launch_delta(const DeltaP& p, int runs, int block, bool pdl, cudaStream_t st) {
-    size_t smem = (size_t)kDrChunk * 5 * p.dk * sizeof(float);
-    if (DK == 0) smem += (size_t)p.dk * block * sizeof(float);
+    const size_t smem = delta_smem(DK, p.dk, p.dv, block);
     if (smem > 48 * 1024) {
         static size_t set_for = 0;
         if (smem > set_for) {
@@ -136,25 +191,32 @@ using namespace zl;
 
 extern "C" int zl_delta_rule_prepare(int dim_k, int dim_v) {
     ZL_CHECK_ARG(dim_k > 0 && dim_v > 0);
-    // the generic kernel keeps its columns in shared memory: a warp of columns must fit beside the token vectors
-    const size_t smem = ((size_t)kDrChunk * 5 * dim_k + (size_t)dim_k * 32) * sizeof(float);
-    ZL_CHECK_SUPPORTED(smem <= 200 * 1024);
+    // the general kernel keeps its columns in shared memory: a warp of columns must fit beside the staged token vectors
+    ZL_CHECK_SUPPORTED(delta_smem(0, dim_k, dim_v, 32) <= 200 * 1024);
     return ZL_OK;
+}
+
+extern "C" size_t zl_delta_rule_workspace_bytes(int T, int heads, int dim_k, int dim_v) {
+    return (size_t)T * heads * (5 * dim_k + dim_v) * sizeof(float);
 }
 
 extern "C" int zl_delta_rule(const float* r, long long ld_r, const float* k, long long ld_k, const float* v, long long ld_v,
                              const float* rate_logit, long long ld_a, const float* decay_logit, long long ld_w,
                              float decay_scale, float unit_eps, const int32_t* run_row0, const int32_t* run_len, int runs,
                              const int32_t* slot, const int32_t* pos, void* const* state_addrs, float* o, long long ld_o,
-                             int heads, int dim_k, int dim_v, int pdl, zl_stream_t stream) {
+                             int heads, int dim_k, int dim_v, int T, void* workspace, size_t workspace_bytes, int pdl,
+                             zl_stream_t stream) {
     ZL_CHECK_ARG(r && k && v && rate_logit && decay_logit && run_row0 && run_len && slot && pos && state_addrs && o);
     ZL_CHECK_ARG(runs > 0 && runs <= 65535 && heads > 0 && heads <= 65535 && dim_k > 0 && dim_v > 0);
+    ZL_CHECK_ARG(T > 0 && T <= 65535 && workspace && workspace_bytes >= zl_delta_rule_workspace_bytes(T, heads, dim_k, dim_v));
     DeltaP p{r, k, v, rate_logit, decay_logit, ld_r, ld_k, ld_v, ld_a, ld_w, run_row0, run_len, slot, pos, state_addrs, o, ld_o,
-             heads, dim_k, dim_v, 0, decay_scale, unit_eps};
+             heads, dim_k, dim_v, 0, decay_scale, unit_eps, static_cast<float*>(workspace)};
+    ZL_CHECK_CUDA(launch(k_delta_prep, dim3(cdiv(heads, 4), T), dim3(128), 0, stream, pdl != 0, p));
     // a warp of columns per CTA spreads one sequence over heads * dv / 32 CTAs
     p.cols = 32;
     const int block = 32;
-    static const bool no_reg = getenv("ZL_DELTA_NO_REG") != nullptr;
+    static const bool no_reg_env = getenv("ZL_DELTA_NO_REG") != nullptr;
+    const bool no_reg = no_reg_env || (5 * dim_k + dim_v) % 4 != 0;   // the register kernel reads the staged vectors 16 bytes at a time
     if (!no_reg && dim_k == 32) return launch_delta<32>(p, runs, block, pdl != 0, stream);
     if (!no_reg && dim_k == 64) return launch_delta<64>(p, runs, block, pdl != 0, stream);
     if (!no_reg && dim_k == 128) return launch_delta<128>(p, runs, block, pdl != 0, stream);

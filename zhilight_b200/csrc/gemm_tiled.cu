@@ -485,7 +485,7 @@ static int grouped_small_max() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("ZL_GEMM_GROUPED_SMALL_MAX");
-        v = e ? atoi(e) : 32;
+        v = e ? atoi(e) : 8;
     }
     return v;
 }

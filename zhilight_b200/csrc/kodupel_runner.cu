@@ -73,6 +73,8 @@ struct zl_kodupel {
     int32_t* h_stage = nullptr;   // pinned: tokens | slots | pos | want | next | run0 | runlen
     void* attn_ws = nullptr;
     size_t attn_ws_bytes = 0;
+    void* delta_ws = nullptr;
+    size_t delta_ws_bytes = 0;
     void* argmax_ws = nullptr;
     float* layer_dump = nullptr;
     bool capture = false;
@@ -273,6 +275,7 @@ int alloc_runtime(zl_kodupel* m) {
         } else {
             RCHECK(zl_delta_rule_prepare(lc.dim, lc.dim));
             RCHECK(L.state.create(B, (size_t)lc.heads * lc.dim * lc.dim * 4, m->stream));
+            m->delta_ws_bytes = std::max(m->delta_ws_bytes, zl_delta_rule_workspace_bytes(T, lc.heads, lc.dim, lc.dim));
             rank = std::max(rank, (size_t)lc.decay_rank);
             hv = std::max(hv, (size_t)lc.heads * lc.dim);
         }
@@ -310,6 +313,7 @@ int alloc_runtime(zl_kodupel* m) {
     RCHECK(dmalloc((void**)&m->list_pair, (size_t)T * top * 4));
     RCHECK(dmalloc((void**)&m->grp_off, (experts + 1) * 4));
     RCHECK(dmalloc(&m->attn_ws, m->attn_ws_bytes));
+    RCHECK(dmalloc(&m->delta_ws, m->delta_ws_bytes));
     RCHECK(dmalloc(&m->argmax_ws, zl_argmax_workspace_bytes(T)));
     ZL_CHECK_CUDA(cudaMallocHost((void**)&m->h_stage, sizeof(int32_t) * 7 * (size_t)T));
     ZL_CHECK_CUDA(cudaStreamSynchronize(m->stream));
@@ -367,7 +371,7 @@ int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_run, int 
             RCHECK(linear(m, m->z1, lc.decay_rank, L.w2, hd, L.w0, L.w0_act, m->dlog, T, ZL_F32, ZL_GEMM_EPI_NONE));
             RCHECK(zl_delta_rule(m->proj + L.q_off, L.n_in, m->proj + L.k_off, L.n_in, m->proj + L.v_off, L.n_in,
                                  m->proj + L.a_off, L.n_in, m->dlog, hd, expf(-0.5f), 1e-6f, m->d_run0, m->d_runlen, n_runs,
-                                 m->d_slots, m->d_pos, L.state.addrs, m->orec, hd, H, lc.dim, lc.dim, 0, st));
+                                 m->d_slots, m->d_pos, L.state.addrs, m->orec, hd, H, lc.dim, lc.dim, T, m->delta_ws, m->delta_ws_bytes, 0, st));
             RCHECK(zl_head_rmsnorm_gate(m->orec, hd, L.out_norm, m->proj + L.g_off, L.n_in, m->att, hd, T, H, lc.dim, c.eps, dt,
                                         0, st));
             RCHECK(linear(m, m->att, hd, L.o, D, nullptr, nullptr, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
@@ -486,7 +490,7 @@ extern "C" void zl_kodupel_destroy(zl_kodupel_t* m) {
                     (void*)m->y, (void*)m->ypair, (void*)m->xw, (void*)m->logits, (void*)m->top_w, m->xa, m->q, m->att, m->z1,
                     m->act, m->xn, (void*)m->d_tokens, (void*)m->d_slots, (void*)m->d_pos, (void*)m->d_want, (void*)m->d_next,
                     (void*)m->d_run0, (void*)m->d_runlen, (void*)m->top_e, (void*)m->grp_off, (void*)m->list_token,
-                    (void*)m->list_pair, m->attn_ws, m->argmax_ws, (void*)m->layer_dump})
+                    (void*)m->list_pair, m->attn_ws, m->delta_ws, m->argmax_ws, (void*)m->layer_dump})
         if (p) cudaFree(p);
     if (m->h_stage) cudaFreeHost(m->h_stage);
     cudaStreamDestroy(m->stream);

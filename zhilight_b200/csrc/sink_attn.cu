@@ -412,11 +412,13 @@ extern "C" size_t zl_sink_attention_workspace_bytes(int T, int heads, int vdim, 
     return splits > 1 ? (size_t)T * heads * splits * (2 + vdim) * sizeof(float) : 0;
 }
 
-// enough CTAs for two waves of the SMs, no split shorter than 256 keys, at most 32
+// enough CTAs for four per SM (a CTA of the tensor-core kernel serves one key/value head of up to 64 / group rows), no
+// split shorter than 128 keys, at most 32
 extern "C" int zl_sink_attention_splits(int T, int heads, int kv_heads, int max_len) {
-    (void)kv_heads;
-    const int want = cdiv(2 * device_sm_count(), T * heads > 0 ? T * heads : 1);
-    const int cap = max_len / 256 > 0 ? max_len / 256 : 1;
+    (void)heads;
+    const int ctas = T * kv_heads > 0 ? T * kv_heads : 1;
+    const int want = cdiv(4 * device_sm_count(), ctas);
+    const int cap = max_len / 128 > 0 ? max_len / 128 : 1;
     int s = want < cap ? want : cap;
     if (s > 32) s = 32;
     return s < 1 ? 1 : s;

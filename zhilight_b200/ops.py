@@ -565,9 +565,11 @@ def delta_rule(r, k, v, rate_logit, decay_logit, decay_scale, unit_eps, run_row0
     """All inputs (T, heads * dim) fp32; state (slots, heads, dim_k, dim_v) fp32 is updated in place.  -> o (T, heads * dim_v)."""
     t = r.shape[0]
     o = torch.empty((t, heads * dim_v), dtype=torch.float32, device=r.device)
+    nbytes = _lib.load().zl_delta_rule_workspace_bytes(t, heads, dim_k, dim_v)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=r.device)
     _lib.call("zl_delta_rule", _p(r), heads * dim_k, _p(k), heads * dim_k, _p(v), heads * dim_v, _p(rate_logit), heads * dim_k,
               _p(decay_logit), heads * dim_k, decay_scale, unit_eps, _p(run_row0), _p(run_len), run_row0.numel(), _p(slot),
-              _p(pos), _p(state_table), _p(o), heads * dim_v, heads, dim_k, dim_v, 0, _stream())
+              _p(pos), _p(state_table), _p(o), heads * dim_v, heads, dim_k, dim_v, t, _p(ws), nbytes, 0, _stream())
     return o
 
 
