@@ -279,9 +279,11 @@ static cudaError_t launch_small_m(const GemmP& p, int batch, int epi, bool pdl, 
 }
 
 // ---- grouped problems with few rows each (decode steps of a mixture of experts) ----------------------------------------
-// One CTA = 32 output columns of one group; the group's rows (gathered through x_rows) sit in shared memory eight at a
+// One CTA = 8 output columns of one group, one per warp; the group's rows (gathered through x_rows) sit in shared memory eight at a
 // time, and a warp streams the weight row of a column -- for the gated unit the gate and the up row of the column -- once
 // per eight rows with four 16-byte loads per row in flight.  Groups without rows cost an early exit.
+constexpr int kGrpCols = 8;
+
 template <typename T, typename TO, bool GLU>
 __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
     extern __shared__ __align__(16) unsigned char sx_raw[];
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
             *reinterpret_cast<uint4*>(sx + (size_t)m * K + k8 * 8) = *reinterpret_cast<const uint4*>(x + row * p.ldx + k8 * 8);
         }
         __syncthreads();
-        for (int n = blockIdx.x * kSmCols + warp; n < min(n_out, (int)(blockIdx.x + 1) * kSmCols); n += 8) {
+        for (int n = blockIdx.x * kGrpCols + warp; n < min(n_out, (int)(blockIdx.x + 1) * kGrpCols); n += 8) {
             float acc[8], acc2[8];
 #pragma unroll
             for (int m = 0; m < 8; ++m) acc[m] = acc2[m] = 0.f;
@@ -354,7 +356,7 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
 
 template <typename T, typename TO>
 static cudaError_t launch_grouped_small(const GemmP& p, int groups, bool glu, bool pdl, cudaStream_t st) {
-    const dim3 grid(cdiv(glu ? p.N / 2 : p.N, kSmCols), groups), block(256);
+    const dim3 grid(cdiv(glu ? p.N / 2 : p.N, kGrpCols), groups), block(256);
     const size_t smem = (size_t)8 * p.K * sizeof(T);
     cudaError_t e = cudaSuccess;
     static size_t set_glu = 0, set_plain = 0;

@@ -156,19 +156,24 @@ __device__ __forceinline__ uint32_t sa_pack(float x, float y) {
     return (uint32_t) * reinterpret_cast<uint16_t*>(&a) | ((uint32_t) * reinterpret_cast<uint16_t*>(&b) << 16);
 }
 
-// grid (ceil(longest run / tokens per tile), G, runs * splits); 4 warps of 16 rows.  NV: 8-column value tiles per warp.
-template <typename T, int NV>
+// grid (ceil(longest run / tokens per tile), G, runs * splits); 4 warps.  NV: 8-column value tiles per warp.
+// DEC = false: a tile of 64 rows, 16 per warp, every warp over all 64 keys of a key tile.
+// DEC = true (the rows of a tile fit 16: decode steps): every warp holds the same 16 rows and takes 16 of the 64 keys
+// of a key tile with a softmax state of its own; the four states are merged through shared memory at the end.
+template <typename T, int NV, bool DEC>
 __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
     extern __shared__ __align__(16) unsigned char sa_raw[];
     const SinkAttnP& p = pp.a;
+    constexpr int QR = DEC ? 16 : kTq;      // rows of the query tile
+    constexpr int NS = DEC ? 2 : 8;         // 8-key score tiles per warp and key tile
     const int DP = p.d + 8, VP = NV * 8 + 8;
-    T* sQ = reinterpret_cast<T*>(sa_raw);   // [kTq][DP]
-    T* sK = sQ + kTq * DP;                  // [2][kTk][DP]
+    T* sQ = reinterpret_cast<T*>(sa_raw);   // [QR][DP]
+    T* sK = sQ + QR * DP;                   // [2][kTk][DP]
     T* sV = sK + 2 * kTk * DP;              // [2][kTk][VP]
     pdl_trigger();
     pdl_wait();
     const int run = blockIdx.z / p.splits, split = blockIdx.z % p.splits, g = blockIdx.y;
-    const int R = p.H / p.G, nq = kTq / R;
+    const int R = p.H / p.G, nq = QR / R;
     const int len = pp.run_len[run], t0 = blockIdx.x * nq;
     if (t0 >= len) return;
     const int ntok = min(nq, len - t0), row0 = pp.run_row0[run] + t0;
@@ -200,12 +205,13 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
             else *reinterpret_cast<uint4*>(dv + (size_t)r * VP + c * 8) = make_uint4(0, 0, 0, 0);
         }
     };
-    // rows of this thread: warp * 16 + gq and + 8; row -> (token, head in the group)
+    // rows of this thread: wrow + gq and + 8; row -> (token, head in the group).  kb: the warp's first key in a key tile
+    const int wrow = DEC ? 0 : warp * 16, kb = DEC ? warp * 16 : 0;
     int tok_of[2], pos_of[2], head_of[2];
     bool row_ok[2];
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-        const int r = warp * 16 + gq + hh * 8;
+        const int r = wrow + gq + hh * 8;
         tok_of[hh] = r / R;
         head_of[hh] = g * R + (r - tok_of[hh] * R);
         row_ok[hh] = tok_of[hh] < ntok;
@@ -215,8 +221,8 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const float sink = p.sink ? p.sink[head_of[hh] < p.H ? head_of[hh] : 0] : 0.f;
-        m_run[hh] = p.splits > 1 ? -1e30f : sink;
-        l_run[hh] = (p.splits > 1 || tq != 0) ? 0.f : 1.f;   // the sink's exp(sink - m) = 1, held by one thread of the quad
+        m_run[hh] = (DEC || p.splits > 1) ? -1e30f : sink;
+        l_run[hh] = (DEC || p.splits > 1 || tq != 0) ? 0.f : 1.f;   // the sink's exp(sink - m) = 1, held by one thread of the quad
     }
 #pragma unroll
     for (int j = 0; j < NV; ++j)
@@ -225,7 +231,7 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
 
     if (k_lo < k_hi) {
         // the query tile
-        for (int i = tid; i < kTq * d8; i += 128) {
+        for (int i = tid; i < QR * d8; i += 128) {
             const int r = i / d8, c = i - r * d8, tk = r / R;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (tk < ntok)
@@ -242,18 +248,18 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
             sa_cp_commit();
             const T* tK = sK + (size_t)buf * kTk * DP;
             const T* tV = sV + (size_t)buf * kTk * VP;
-            float S[8][4];
+            float S[NS][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < NS; ++j)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) S[j][c] = 0.f;
             for (int kk = 0; kk < p.d; kk += 16) {
                 uint32_t a[4];
-                sa_ldmatrix_x4(a, sQ + (size_t)(warp * 16 + (lane & 15)) * DP + kk + (lane >> 4) * 8);
+                sa_ldmatrix_x4(a, sQ + (size_t)(wrow + (lane & 15)) * DP + kk + (lane >> 4) * 8);
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
+                for (int jj = 0; jj < NS / 2; ++jj) {
                     uint32_t b[4];
-                    sa_ldmatrix_x4(b, tK + (size_t)(jj * 16 + (lane & 7) + (lane >> 4) * 8) * DP + kk + ((lane >> 3) & 1) * 8);
+                    sa_ldmatrix_x4(b, tK + (size_t)(kb + jj * 16 + (lane & 7) + (lane >> 4) * 8) * DP + kk + ((lane >> 3) & 1) * 8);
                     sa_mma<T>(S[2 * jj], a, b[0], b[1]);
                     sa_mma<T>(S[2 * jj + 1], a, b[2], b[3]);
                 }
@@ -261,10 +267,10 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
             // scale, mask, online softmax (rows gq and gq + 8 of the warp's 16)
             float mx[2] = {-1e30f, -1e30f};
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < NS; ++j)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const int hh = c >> 1, key = k0 + 8 * j + 2 * tq + (c & 1);
+                    const int hh = c >> 1, key = k0 + kb + 8 * j + 2 * tq + (c & 1);
                     const bool ok = row_ok[hh] && key < k_hi && key <= pos_of[hh];
                     S[j][c] = ok ? S[j][c] * p.scale : -1e30f;
                     mx[hh] = fmaxf(mx[hh], S[j][c]);
@@ -280,7 +286,7 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
                 l_run[hh] *= corr[hh];
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < NS; ++j)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int hh = c >> 1;
@@ -295,7 +301,7 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
             }
             // O += P V, 16 keys at a time
 #pragma unroll
-            for (int k2 = 0; k2 < 4; ++k2) {
+            for (int k2 = 0; k2 < NS / 2; ++k2) {
                 uint32_t ah[4], al[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
@@ -309,7 +315,7 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
 #pragma unroll
                 for (int nn = 0; nn < NV / 2; ++nn) {
                     uint32_t b[4];
-                    sa_ldmatrix_x4_trans(b, tV + (size_t)(k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + nn * 16 + (lane >> 4) * 8);
+                    sa_ldmatrix_x4_trans(b, tV + (size_t)(kb + k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VP + nn * 16 + (lane >> 4) * 8);
                     sa_mma<T>(O[2 * nn], ah, b[0], b[1]);
                     sa_mma<T>(O[2 * nn + 1], ah, b[2], b[3]);
                     if constexpr (!std::is_same<T, __half>::value) {
@@ -325,6 +331,54 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
         l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
         l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
     }
+    if constexpr (DEC) {
+        // the four warps' states of the same 16 rows -> one, through shared memory (the key tiles are no longer needed)
+        __syncthreads();
+        float* mm = reinterpret_cast<float*>(sa_raw);   // [4][16] max, [4][16] sum, [4][16][NV * 8] values
+        float* ml = mm + 64;
+        float* mo = ml + 64;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int r = gq + hh * 8;
+            if (tq == 0) mm[warp * 16 + r] = m_run[hh], ml[warp * 16 + r] = l_run[hh];
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                mo[((size_t)warp * 16 + r) * (NV * 8) + 8 * j + 2 * tq] = O[j][hh * 2];
+                mo[((size_t)warp * 16 + r) * (NV * 8) + 8 * j + 2 * tq + 1] = O[j][hh * 2 + 1];
+            }
+        }
+        __syncthreads();
+        const int r = tid >> 3, tk = r / R;   // 8 threads per row
+        if (tk >= ntok) return;
+        const int t = row0 + tk, h = g * R + (r - tk * R);
+        const float sink = p.sink ? p.sink[h] : 0.f;
+        float M = p.splits > 1 ? -1e30f : sink;
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[w * 16 + r]);
+        float L = p.splits > 1 ? 0.f : expf(sink - M), wgt[4];
+        for (int w = 0; w < 4; ++w) {
+            wgt[w] = ml[w * 16 + r] > 0.f ? expf(mm[w * 16 + r] - M) : 0.f;
+            L = fmaf(ml[w * 16 + r], wgt[w], L);
+        }
+        if (p.splits > 1) {
+            float* part = p.ws + (((size_t)t * p.H + h) * p.splits + split) * (2 + p.vd);
+            if ((tid & 7) == 0) part[0] = L > 0.f ? M : -INFINITY, part[1] = L;
+            for (int c = tid & 7; c < p.vd; c += 8) {
+                float o = 0.f;
+                for (int w = 0; w < 4; ++w) o = fmaf(mo[((size_t)w * 16 + r) * (NV * 8) + c], wgt[w], o);
+                part[2 + c] = o;
+            }
+        } else {
+            float gate = 1.0f;
+            if (p.gate) gate = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.ldg + h]));
+            const float inv = gate / L;
+            T* out = static_cast<T*>(p.out) + ((size_t)t * p.H + h) * p.vd;
+            for (int c = tid & 7; c < p.vd; c += 8) {
+                float o = 0.f;
+                for (int w = 0; w < 4; ++w) o = fmaf(mo[((size_t)w * 16 + r) * (NV * 8) + c], wgt[w], o);
+                out[c] = from_f32<T>(o * inv);
+            }
+        }
+    } else {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         if (!row_ok[hh]) continue;
@@ -353,26 +407,34 @@ __global__ void __launch_bounds__(128) k_sink_attn_mma(SinkAttnMmaP pp) {
             }
         }
     }
+    }
 }
 
-template <typename T, int NV>
+template <typename T, int NV, bool DEC>
 static cudaError_t launch_sink_mma(const SinkAttnMmaP& pp, int runs, int max_run_len, bool pdl, cudaStream_t st) {
     const SinkAttnP& p = pp.a;
-    const int nq = kTq / (p.H / p.G);
-    const size_t smem = ((size_t)kTq * (p.d + 8) + 2 * (size_t)kTk * (p.d + 8) + 2 * (size_t)kTk * (NV * 8 + 8)) * sizeof(T);
+    const int qr = DEC ? 16 : kTq, nq = qr / (p.H / p.G);
+    size_t smem = ((size_t)qr * (p.d + 8) + 2 * (size_t)kTk * (p.d + 8) + 2 * (size_t)kTk * (NV * 8 + 8)) * sizeof(T);
+    if (DEC && smem < (size_t)(128 + 64 * NV * 8) * sizeof(float)) smem = (size_t)(128 + 64 * NV * 8) * sizeof(float);
     static size_t set_for = 0;
     if (smem > 48 * 1024 && smem > set_for) {
-        const cudaError_t e = cudaFuncSetAttribute(k_sink_attn_mma<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(k_sink_attn_mma<T, NV, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         set_for = smem;
     }
-    return launch(k_sink_attn_mma<T, NV>, dim3(cdiv(max_run_len, nq), p.G, runs * p.splits), dim3(128), smem, st, pdl, pp);
+    return launch(k_sink_attn_mma<T, NV, DEC>, dim3(cdiv(max_run_len, nq), p.G, runs * p.splits), dim3(128), smem, st, pdl, pp);
+}
+template <typename T, int NV>
+static cudaError_t launch_sink_mma_d(const SinkAttnMmaP& pp, int runs, int max_run_len, bool pdl, cudaStream_t st) {
+    // the rows of the longest run fit one 16-row tile: the decode form
+    if (max_run_len * (pp.a.H / pp.a.G) <= 16) return launch_sink_mma<T, NV, true>(pp, runs, max_run_len, pdl, st);
+    return launch_sink_mma<T, NV, false>(pp, runs, max_run_len, pdl, st);
 }
 template <typename T>
 static cudaError_t launch_sink_mma_t(const SinkAttnMmaP& pp, int runs, int max_run_len, bool pdl, cudaStream_t st) {
-    if (pp.a.vd <= 32) return launch_sink_mma<T, 4>(pp, runs, max_run_len, pdl, st);
-    if (pp.a.vd <= 64) return launch_sink_mma<T, 8>(pp, runs, max_run_len, pdl, st);
-    return launch_sink_mma<T, 16>(pp, runs, max_run_len, pdl, st);
+    if (pp.a.vd <= 32) return launch_sink_mma_d<T, 4>(pp, runs, max_run_len, pdl, st);
+    if (pp.a.vd <= 64) return launch_sink_mma_d<T, 8>(pp, runs, max_run_len, pdl, st);
+    return launch_sink_mma_d<T, 16>(pp, runs, max_run_len, pdl, st);
 }
 
 // merge of the splits with the sink term and the gate; one warp per (token, head), grid (ceil(H / 4), T)
@@ -442,7 +504,7 @@ extern "C" int zl_sink_attention(const void* q, void* const* k_addrs, void* cons
     cudaError_t e;
     static const bool no_mma = getenv("ZL_SINK_ATTN_NO_MMA") != nullptr;
     const bool mma = !no_mma && run_row0 && run_len && runs > 0 && max_run_len > 0 && dtype != ZL_F32 && dim % 16 == 0 &&
-                     vdim % 8 == 0 && vdim <= 128 && dim <= 256 && heads / kv_heads <= 16 && kTq % (heads / kv_heads) == 0;
+                     vdim % 8 == 0 && vdim <= 128 && dim <= 256 && heads / kv_heads <= 16 && 16 % (heads / kv_heads) == 0;
     if (mma) {
         ZL_CHECK_ARG((long long)runs * splits <= 65535 && kv_heads <= 65535);
         SinkAttnMmaP pp{p, run_row0, run_len};
