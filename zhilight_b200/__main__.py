@@ -11,9 +11,13 @@ import os
 import sys
 
 
-def _build():
-    from . import build
-    return build.build()
+def _build(family=None):
+    """The whole library, or -- in a checkout without it -- only what `family` needs."""
+    from . import _lib, build
+    path = build.build(family=family)
+    if path != build.LIB_PATH:
+        _lib.use(path)
+    return path
 
 
 def main(argv=None):
@@ -50,7 +54,8 @@ def main(argv=None):
         if a.dtype not in registry.supported_dtypes(config):
             sys.stderr.write("%s does not run in %s\n" % (registry.architecture_of(config), a.dtype))
             return 3
-    _build()
+    with open(os.path.join(a.model, "config.json")) as f:
+        _build(family=str(registry.architecture_of(json.load(f))))
     if a.cmd == "generate":
         from .engine import Engine, SamplingParams
         prompts = [[int(x) for x in p.split(",") if x.strip()] for p in a.prompt_ids]

@@ -110,17 +110,34 @@ _lib = None
 _protos = None
 
 
+_path = None
+
+
+def use(path):
+    """Bind `path` instead of the whole library: a library built from one family's sources (build.build(family=...)).
+    Must be called before the first load()."""
+    global _path
+    if _lib is not None and os.path.abspath(path) != os.path.abspath(_path or LIB_PATH):
+        raise ZLError(-100, "a library is already loaded")
+    _path = path
+
+
 def load():
     """Load the library (building nothing).  Raises if the .so is absent."""
     global _lib, _protos
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
-        raise ZLError(-100, "libzhilight_b200.so not built (run `python -m zhilight_b200.build`); "
-                            "there is no CPU fallback")
-    lib = ctypes.CDLL(LIB_PATH)
+    path = _path or LIB_PATH
+    if not os.path.exists(path):
+        raise ZLError(-100, "%s not built (run `python -m zhilight_b200.build`); there is no CPU fallback"
+                      % os.path.basename(path))
+    lib = ctypes.CDLL(path)
     _protos = parse_header()
-    for name, (ret, params) in _protos.items():
+    partial = os.path.abspath(path) != os.path.abspath(LIB_PATH)
+    for name, (ret, params) in list(_protos.items()):
+        if partial and not hasattr(lib, name):
+            del _protos[name]            # a family library has only its own entry points; calling another raises AttributeError
+            continue
         fn = getattr(lib, name)          # AttributeError if the symbol is missing
         fn.restype = ctypes.c_char_p if ret.replace("const", "").strip() == "char*" else _ctype(ret)
         fn.argtypes = [_ctype(t) for t, _ in params]

@@ -1,6 +1,11 @@
 """In-tree build of libzhilight_b200.so (sm_100a only).  nvcc cross-compiles without a GPU.
 
-    python -m zhilight_b200.build [--force] [--verbose]
+    python -m zhilight_b200.build [--force] [--verbose] [--family NAME]
+
+`build()` makes the whole library.  `build(family=...)` serves a program that runs one model family in a checkout
+without built files: when the whole library is present and current it is returned, otherwise only the sources that
+family's step needs are compiled and linked into libzhilight_b200_<family>.so (the binding skips the entry points such
+a library does not have).
 """
 import hashlib
 import os
@@ -22,6 +27,18 @@ NVCC_FLAGS = [
     "-Xptxas", "-v",
     "-DZL_BUILD",
 ]
+
+
+# sources of the families whose drivers stand on their own (names without .cu)
+_FP32_RESIDUAL_COMMON = ["misc", "dense_gemm", "gemm_tiled", "group_norm_conv"]
+FAMILY_SOURCES = {
+    "kodupel": _FP32_RESIDUAL_COMMON + ["mixer_rows", "moe_route", "delta_rule", "sink_attn", "kodupel_runner"],
+    "dekipel": _FP32_RESIDUAL_COMMON + ["latent_attn", "dekipel_runner"],
+}
+
+
+def family_lib_path(family):
+    return os.path.join(HERE, "libzhilight_b200_%s.so" % family)
 
 
 def _nvcc():
@@ -50,18 +67,27 @@ def _digest(paths):
     return h.hexdigest()
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, family=None):
     # fast path: the shipped .so already matches the sources (e.g. on the GPU box, where build/ is not shipped)
     all_digest = _digest(_sources() + _headers())
     dig_path = LIB_PATH + ".digest"
     if not force and os.path.exists(LIB_PATH) and os.path.exists(dig_path) and open(dig_path).read() == all_digest:
         return LIB_PATH
+    sources, lib_path = _sources(), LIB_PATH
+    family = (family or "").lower()
+    if family in FAMILY_SOURCES:
+        sources = [os.path.join(CSRC, n + ".cu") for n in FAMILY_SOURCES[family]]
+        lib_path = family_lib_path(family)
+        all_digest = _digest(sources + _headers())
+        dig_path = lib_path + ".digest"
+        if not force and os.path.exists(lib_path) and os.path.exists(dig_path) and open(dig_path).read() == all_digest:
+            return lib_path
     os.makedirs(OBJ_DIR, exist_ok=True)
     nvcc = _nvcc()
     hdr_digest = _digest(_headers())
     jobs = []
     objs = []
-    for src in _sources():
+    for src in sources:
         name = os.path.splitext(os.path.basename(src))[0]
         obj = os.path.join(OBJ_DIR, name + ".o")
         stamp = obj + ".stamp"
@@ -89,17 +115,18 @@ def build(force=False, verbose=False):
             for src, log in ex.map(compile_one, jobs):
                 if verbose:
                     print("== %s\n%s" % (os.path.basename(src), log))
-    if jobs or force or not os.path.exists(LIB_PATH):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
+    if jobs or force or not os.path.exists(lib_path):
+        cmd = [nvcc, "-shared", "-o", lib_path] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
                                                           "-lcudart", "-Xlinker", "--no-undefined"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
     with open(dig_path, "w") as f:
         f.write(all_digest)
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    fam = sys.argv[sys.argv.index("--family") + 1] if "--family" in sys.argv else None
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, family=fam)
     print(path)

@@ -344,7 +344,6 @@ extern "C" int zl_dekipel_create(const zl_dekipel_config_t* cfg, const zl_dekipe
             ZL_CHECK_ARG(lc.kv_from < l && layers[lc.kv_from].kv_from < 0 && layers[lc.kv_from].kv_rank == lc.kv_rank);
         }
     }
-    RCHECK(zl_prepare());
     zl_dekipel* m = new zl_dekipel();
     m->cfg = *cfg;
     m->esz = cfg->dtype == ZL_F32 ? 4 : 2;

@@ -456,7 +456,6 @@ extern "C" int zl_kodupel_create(const zl_kodupel_config_t* cfg, const zl_kodupe
         }
         if (lc.experts > 0) ZL_CHECK_ARG(lc.top > 0 && lc.top <= lc.experts && lc.ff > 0 && lc.limit > 0.f);
     }
-    RCHECK(zl_prepare());
     zl_kodupel* m = new zl_kodupel();
     m->cfg = *cfg;
     m->esz = cfg->dtype == ZL_F32 ? 4 : 2;

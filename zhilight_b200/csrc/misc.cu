@@ -23,6 +23,10 @@ extern "C" long long zl_launch_count(int reset) {
     return v;
 }
 
+// debug timeline buffer of the decode chains (zl_w4_set_trace); lives here so that a library built from a subset of
+// the sources still links
+unsigned long long* g_w4_trace = nullptr;
+
 namespace zl {
 
 // out[t, :] = table[ids[t], :]   (16-byte chunks)
