@@ -184,7 +184,7 @@ def test_head_norms_rotation_and_cache_append(cuda, lib, dtype):
 def test_sink_attention_far_key_sink_and_groups(cuda, lib, dtype, H):
     """700 keys.  One far key is made to carry the softmax of one head (query and that key scaled up), another head's
     scores are pushed far below zero so that the unit sink takes the whole denominator; rows past a token's position
-    hold huge values that must not be seen; key splits 1 / 2 / 5.  Each query row alone and as runs of consecutive rows
+    hold huge values that must not be seen; key splits 1 / 2 / 5 / 23.  Each query row alone and as runs of consecutive rows
     (the tensor-core kernel tiles the tokens of a run; 8 heads on 2 key/value heads fit its tile, 6 do not)."""
     import torch
     from zhilight_b200 import ops
@@ -208,7 +208,7 @@ def test_sink_attention_far_key_sink_and_groups(cuda, lib, dtype, H):
     kc[1, :n] = dev(k.reshape(n, -1), cuda, td)
     vc[1, :n] = dev(v.reshape(n, -1), cuda, td)
     tol = 1e-5 if dtype == "float32" else 1e-2
-    for splits in (1, 2, 5):
+    for splits in (1, 2, 5, 23):
         # every query row alone: its keys end at its own position, the rows behind it are poison
         out = ops.sink_attention(dev(q[rows].reshape(len(rows), -1), cuda, td), ops.slot_table(kc), ops.slot_table(vc),
                                  i32([1] * len(rows), cuda), i32(rows, cuda), scale, H, G, d, vd, gate=dev(gate[rows], cuda),

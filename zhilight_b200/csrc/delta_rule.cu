@@ -17,7 +17,7 @@
 
 namespace zl {
 
-constexpr int kDrChunk = 16;   // tokens staged at a time
+constexpr int kDrChunk = 16;   // tokens staged at a time (fewer when a head's vectors are too large for two such buffers)
 
 struct DeltaP {
     const float *r, *k, *v, *rate_logit, *decay_logit;   // (T, H * dk) / v: (T, H * dv), row strides below
@@ -30,6 +30,7 @@ struct DeltaP {
     int H, dk, dv, cols;
     float decay_scale, unit_eps;
     float* prep;                         // (T, H, 5 * dk + dv): u, a*u, w, k, r, v of every token and head
+    int chunk;                           // tokens staged at a time
 };
 
 // The token vectors of the recurrence, for all tokens at once: one warp per (token, head).  grid (ceil(H / 4), T)
@@ -75,7 +76,7 @@ __global__ void k_delta_rule(DeltaP p) {
     const int dk = DK > 0 ? DK : p.dk;
     const int per = 5 * dk + p.dv;                      // floats per (token, head)
     float* tok = dsm;                                   // [2][kDrChunk][per]
-    float* scol = dsm + (size_t)2 * kDrChunk * per;     // DK == 0: [dk][blockDim] the columns of this CTA
+    float* scol = dsm + (size_t)2 * p.chunk * per;      // DK == 0: [dk][blockDim] the columns of this CTA
     pdl_trigger();
     pdl_wait();
     const int run = blockIdx.z, h = blockIdx.y, tid = threadIdx.x, nth = blockDim.x;
@@ -87,8 +88,8 @@ __global__ void k_delta_rule(DeltaP p) {
     const bool fresh = p.pos[row0] == 0;
     const bool vec = (per & 3) == 0;
     auto stage = [&](int buf, int c0) {
-        const int cn = min(kDrChunk, len - c0);
-        float* dst = tok + (size_t)buf * kDrChunk * per;
+        const int cn = min(p.chunk, len - c0);
+        float* dst = tok + (size_t)buf * p.chunk * per;
         for (int tt = 0; tt < cn; ++tt) {
             const float* src = p.prep + ((size_t)(row0 + c0 + tt) * p.H + h) * per;
             if (vec)
@@ -109,16 +110,16 @@ __global__ void k_delta_rule(DeltaP p) {
         }
     }
     int buf = 0;
-    for (int c0 = 0; c0 < len; c0 += kDrChunk, buf ^= 1) {
-        const int cn = min(kDrChunk, len - c0);
+    for (int c0 = 0; c0 < len; c0 += p.chunk, buf ^= 1) {
+        const int cn = min(p.chunk, len - c0);
         dr_cp_wait_all();
         __syncthreads();   // this chunk has landed for every thread; the other half is no longer read
-        if (c0 + kDrChunk < len) stage(buf ^ 1, c0 + kDrChunk);
+        if (c0 + p.chunk < len) stage(buf ^ 1, c0 + p.chunk);
         dr_cp_commit();
         if (!mine) continue;
         for (int tt = 0; tt < cn; ++tt) {
             const size_t t = (size_t)(row0 + c0 + tt);
-            const float* tv = tok + ((size_t)buf * kDrChunk + tt) * per;
+            const float* tv = tok + ((size_t)buf * p.chunk + tt) * per;
             const float vj = tv[5 * dk + blockIdx.x * p.cols + tid];
             float out = 0.f;
             if constexpr (DK > 0) {
@@ -165,8 +166,14 @@ __global__ void k_delta_rule(DeltaP p) {
     }
 }
 
+// tokens per staging buffer: kDrChunk, or as many as keep the two buffers within 96 KB (at least one)
+static int delta_chunk(int dk, int dv) {
+    const size_t per = (size_t)(5 * dk + dv) * sizeof(float);
+    size_t c = (96 * 1024) / (2 * per);
+    return c >= (size_t)kDrChunk ? kDrChunk : (c < 1 ? 1 : (int)c);
+}
 static size_t delta_smem(int DK, int dk, int dv, int block) {
-    size_t smem = (size_t)2 * kDrChunk * (5 * dk + dv) * sizeof(float);
+    size_t smem = (size_t)2 * delta_chunk(dk, dv) * (5 * dk + dv) * sizeof(float);
     if (DK == 0) smem += (size_t)dk * block * sizeof(float);
     return smem;
 }
@@ -210,7 +217,7 @@ extern "C" int zl_delta_rule(const float* r, long long ld_r, const float* k, lon
     ZL_CHECK_ARG(runs > 0 && runs <= 65535 && heads > 0 && heads <= 65535 && dim_k > 0 && dim_v > 0);
     ZL_CHECK_ARG(T > 0 && T <= 65535 && workspace && workspace_bytes >= zl_delta_rule_workspace_bytes(T, heads, dim_k, dim_v));
     DeltaP p{r, k, v, rate_logit, decay_logit, ld_r, ld_k, ld_v, ld_a, ld_w, run_row0, run_len, slot, pos, state_addrs, o, ld_o,
-             heads, dim_k, dim_v, 0, decay_scale, unit_eps, static_cast<float*>(workspace)};
+             heads, dim_k, dim_v, 0, decay_scale, unit_eps, static_cast<float*>(workspace), delta_chunk(dim_k, dim_v)};
     ZL_CHECK_CUDA(launch(k_delta_prep, dim3(cdiv(heads, 4), T), dim3(128), 0, stream, pdl != 0, p));
     // a warp of columns per CTA spreads one sequence over heads * dv / 32 CTAs
     p.cols = 32;

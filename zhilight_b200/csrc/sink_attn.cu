@@ -437,32 +437,35 @@ static cudaError_t launch_sink_mma_t(const SinkAttnMmaP& pp, int runs, int max_r
     return launch_sink_mma_d<T, 16>(pp, runs, max_run_len, pdl, st);
 }
 
-// merge of the splits with the sink term and the gate; one warp per (token, head), grid (ceil(H / 4), T)
+// merge of the splits (at most 32) with the sink term and the gate; one warp per (token, head), grid (ceil(H / 4), T).
+// Lane s holds the (max, sum) of split s, so the weights of all splits come from one round of loads.
 template <typename T>
 __global__ void __launch_bounds__(128) k_sink_attn_merge(SinkAttnP p) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.y, h = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (h >= p.H) return;
-    const float* part = p.ws + ((size_t)t * p.H + h) * p.splits * (2 + p.vd);
+    const int stride = 2 + p.vd;
+    const float* part = p.ws + ((size_t)t * p.H + h) * p.splits * stride;
     const float sink = p.sink ? p.sink[h] : 0.f;
-    float M = sink;
-    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, part[(size_t)s * (2 + p.vd)]);
+    const float ms = lane < p.splits ? part[(size_t)lane * stride] : -INFINITY;
+    const float ls = lane < p.splits ? part[(size_t)lane * stride + 1] : 0.f;
+    const float M = fmaxf(sink, warp_max(ms));
+    const float wgt = ms == -INFINITY ? 0.f : expf(ms - M);
+    // the sum over the splits in the order of the splits, the same in every lane
     float L = expf(sink - M);
-    for (int s = 0; s < p.splits; ++s) {
-        const float ms = part[(size_t)s * (2 + p.vd)];
-        L = fmaf(part[(size_t)s * (2 + p.vd) + 1], ms == -INFINITY ? 0.f : expf(ms - M), L);
-    }
+    for (int s = 0; s < p.splits; ++s) L = fmaf(__shfl_sync(0xffffffffu, ls, s), __shfl_sync(0xffffffffu, wgt, s), L);
     float gate = 1.0f;
     if (p.gate) gate = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.ldg + h]));
     T* out = static_cast<T*>(p.out) + ((size_t)t * p.H + h) * p.vd;
-    for (int c = lane; c < p.vd; c += 32) {
+    for (int c0 = 0; c0 < p.vd; c0 += 32) {   // every lane runs the shuffles; only lanes with a column load and store
+        const int c = c0 + lane;
         float o = 0.f;
         for (int s = 0; s < p.splits; ++s) {
-            const float ms = part[(size_t)s * (2 + p.vd)];
-            o = fmaf(part[(size_t)s * (2 + p.vd) + 2 + c], ms == -INFINITY ? 0.f : expf(ms - M), o);
+            const float w = __shfl_sync(0xffffffffu, wgt, s);
+            if (c < p.vd) o = fmaf(part[(size_t)s * stride + 2 + c], w, o);
         }
-        out[c] = from_f32<T>(o / L * gate);
+        if (c < p.vd) out[c] = from_f32<T>(o / L * gate);
     }
 }
 
@@ -495,7 +498,7 @@ extern "C" int zl_sink_attention(const void* q, void* const* k_addrs, void* cons
     ZL_CHECK_ARG(heads % kv_heads == 0 && dim > 0 && vdim > 0);
     ZL_CHECK_SUPPORTED(vdim <= 32 * kSaMaxPerLane);
     ZL_CHECK_ARG(dtype == ZL_F16 || dtype == ZL_BF16 || dtype == ZL_F32);
-    ZL_CHECK_ARG(splits >= 1 && splits <= 65535);
+    ZL_CHECK_ARG(splits >= 1 && splits <= 32);
     ZL_CHECK_ARG(splits == 1 || (workspace && workspace_bytes >= zl_sink_attention_workspace_bytes(T, heads, vdim, splits)));
     SinkAttnP p{q, k_addrs, v_addrs, slot, pos, sink, gate, ldg, out, heads, kv_heads, dim, vdim, scale, splits,
                 static_cast<float*>(workspace)};
