@@ -452,7 +452,7 @@ KODUPEL_SIZES = {
 def _kodupel_config(sz):
     moe = {"kind": "moe", "expert": {"ff": sz["ff_e"], "limit": 7.0}, "router": {"experts": sz["experts"], "top": sz["top"]}}
     att = dict(heads=sz["heads"], kv_heads=8, dim=sz["dim"], vdim=sz["dim"], scale=sz["dim"] ** -0.5,
-               rot={"base": 1e6, "dims": sz["dim"] // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}})
+               rot={"base": 5e5, "dims": sz["dim"] // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 24.0, "slow": 2.0}})
     layers = []
     for i in range(sz["layers"]):
         if i % 4 == 2:

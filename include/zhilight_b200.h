@@ -530,8 +530,8 @@ int zl_qkv_headnorm_rope_append(const float* proj, long long ldp, int q_off, int
                                 void* const* v_addrs, const int32_t* slot, const int32_t* pos, int T, int dtype, int pdl,
                                 zl_stream_t stream);
 /* Causal attention over the slots' caches: query head h uses key/value head h / (heads / kv_heads);
- * p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i)) with s = scale * q . k (sink NULL: 0, i.e. one added to the
- * denominator); out (T, heads * vdim) of `dtype`, head h times sigmoid(gate[t * ldg + h]) when gate != NULL.
+ * p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i)) with s = scale * q . k (sink NULL: every sink is 0, the
+ * extra term is then exactly 1); out (T, heads * vdim) of `dtype`, head h times sigmoid(gate[t * ldg + h]) when gate != NULL.
  * splits > 1 cuts the keys of every token over that many CTAs (decode with long contexts); workspace of
  * zl_sink_attention_workspace_bytes.  With the runs of the step (run i = rows run_row0[i] .. + run_len[i]: one slot,
  * consecutive positions; max_run_len bounds run_len) 16-bit caches go through the tensor-core kernel, which tiles
@@ -576,7 +576,7 @@ int zl_moe_route(const float* x, long long ldx, const float* w_router, const flo
 /* ------------------------------------------------------------------------------------------ *
  * Kodupel: decoder-only model whose layers are listed one by one: the mixer is attention (grouped key/value heads,
  * biased projections, per-head query / key RMS norm, partial rotation in adjacent pairs with YaRN frequencies, value
- * heads of unit RMS, a softmax with one added to the denominator, one sigmoid gate per head, optionally another
+ * heads of unit RMS, a softmax whose denominator holds an extra 1, one sigmoid gate per head, optionally another
  * layer's key/value cache) or a generalized delta rule (a recurrent per-head state); the feed-forward is a mixture
  * of clamped gated experts chosen by sigmoid scores plus a correction; RMS norms with weight 1 + w sit on the
  * sublayers' outputs only; the residual stream is fp32.  Same driver shape as zl_dekipel_*.

@@ -19,7 +19,7 @@ def unit_rms(x, eps):
 
 
 def out_norm(y, w, eps):
-    """RMS norm whose stored weight sits around zero."""
+    """RMS norm times (1 + w): the checkpoint keeps w, not the multiplier."""
     return unit_rms(y, eps) * (1.0 + w)
 
 

@@ -37,15 +37,15 @@ def E(experts, top, ff, limit):
     return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
 
 
-YARN_A, YARN_C = (4.0, 64, 16.0, 2.0), (2.0, 40, 8.0, 0.5)
+YARN_A, YARN_C = (4.0, 64, 16.0, 2.0), (3.0, 40, 8.0, 0.5)
 CFG_MIXED = {"architecture": "Kodupel", "vocab": 67, "width": 48, "embedding": {"scale": 2.5}, "norm": {"eps": 1e-5},
              "layers": [A(4, 2, 12, 8, 0.3, 8, scaling=YARN_A, moe=E(5, 2, 20, 1.5)), R(3, 16, 5),
                         A(4, 2, 12, 8, 0.3, 8, scaling=YARN_A, kv_from=0, moe=E(3, 1, 24, 0.7)), R(2, 24, 7, moe=E(4, 4, 12, 2.0))]}
 CFG_ONES = {"architecture": "Kodupel", "vocab": 40, "width": 32, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
             "layers": [R(1, 32, 3, moe=E(1, 1, 16, 1.0)), A(1, 1, 32, 16, 0.17, 32, base=500.0)]}
 CFG_WIDE = {"architecture": "Kodupel", "vocab": 96, "width": 64, "embedding": {"scale": 4.0}, "norm": {"eps": 1e-5},
-            "layers": [A(8, 2, 16, 32, 0.25, 4, base=1e6, scaling=YARN_C, moe=E(8, 3, 40, 1.0)), R(2, 64, 8, moe=E(8, 3, 40, 1.0)),
-                       A(8, 2, 16, 32, 0.25, 4, base=1e6, scaling=YARN_C, kv_from=0)]}
+            "layers": [A(8, 2, 16, 32, 0.25, 4, base=2e5, scaling=YARN_C, moe=E(8, 3, 40, 1.0)), R(2, 64, 8, moe=E(8, 3, 40, 1.0)),
+                       A(8, 2, 16, 32, 0.25, 4, base=2e5, scaling=YARN_C, kv_from=0)]}
 CONFIGS = {"mixed": CFG_MIXED, "ones": CFG_ONES, "wide": CFG_WIDE}
 
 
@@ -138,7 +138,7 @@ def _grouped_case(cuda, td, tol, rng, T, sizes):
 
 def test_rotation_frequencies(lib):
     from zhilight_b200 import ops
-    for base, dims, sc in ((10000.0, 8, YARN_A), (1e6, 4, YARN_C), (500.0, 32, None), (1e4, 64, (8.0, 4096, 32.0, 1.0))):
+    for base, dims, sc in ((10000.0, 8, YARN_A), (2e5, 4, YARN_C), (500.0, 32, None), (1e4, 64, (8.0, 4096, 24.0, 2.0))):
         f, ms = ops.rope_inv_freq_yarn(base, dims, *(sc or ()))
         scd = dict(zip(("factor", "original", "fast", "slow"), sc)) if sc else None
         cos, sin = orc.rotation_tables(2, dims, base, scd)

@@ -105,7 +105,7 @@ __global__ void k_interleave_rows(const TS* __restrict__ gate, const TS* __restr
     dst[(2 * j + 1) * D + c] = from_f32<TD>(to_f32<TS>(up[i]));
 }
 
-// norm weight stored around zero -> fp32 array of 1 + w
+// checkpoint norm tensor w -> fp32 array of the multipliers 1 + w
 int take_norm(zl_kodupel* m, const std::string& name, int n, float** out) {
     RCHECK(take_f32(m, name, 1, n, out));
     k_add_one<<<cdiv(n, 256), 256, 0, m->stream>>>(*out, n);

@@ -6,7 +6,7 @@ x = embedding.scale * embed[token].  Mixers:
 
   * "attention": grouped key/value heads, biased q / k / v / o projections, RMS norm per head on queries and keys,
     rotation of the first rot.dims dimensions in adjacent pairs with YaRN-scaled frequencies, value heads of unit RMS,
-    a causal softmax with one added to the denominator, one sigmoid gate per head; "kv_from": j reads layer j's cache;
+    a causal softmax whose denominator holds an extra 1, one sigmoid gate per head; "kv_from": j reads layer j's cache;
   * "general_delta": per head a (dim, dim) fp32 state S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r, then per-head
     RMS norm, a weight, a sigmoid gate and the output projection.
 
