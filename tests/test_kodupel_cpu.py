@@ -98,3 +98,14 @@ def test_oracle_mechanisms_by_hand():
     assert np.isclose(orc.expert(W, "", np.array([1.0]), 2.0)[0], 2.0 * orc.sigmoid(1.702 * 2.0) * (-2.0 + 1.0))
     chosen, weight = orc.route(np.array([[1.0]]), np.array([[0.0], [2.0]]), np.array([5.0, 0.0]), 1)
     assert chosen[0, 0] == 0 and np.isclose(weight[0, 0], 0.5)
+
+
+def test_family_libraries_name_existing_sources():
+    """A checkout without built files compiles only a family's sources: they must exist, and hold the family's driver."""
+    import os
+    from zhilight_b200 import build
+    for family, names in build.FAMILY_SOURCES.items():
+        assert family + "_runner" in names and "misc" in names
+        for n in names:
+            assert os.path.exists(os.path.join(build.CSRC, n + ".cu")), (family, n)
+        assert build.family_lib_path(family).endswith("libzhilight_b200_%s.so" % family)
