@@ -91,6 +91,20 @@ int fail(int line, const std::string& msg, int code = ZL_ERR_STATE) {
     return code;
 }
 
+// x[t] = scale * embed[token[t]] in fp32 and the same rounded to the activation dtype (what the first Linears read)
+__global__ void k_embed_scaled_pair(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table, float* __restrict__ x,
+                                    __nv_bfloat16* __restrict__ xa, int D, int vocab, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    int id = ids[blockIdx.x];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = __bfloat162float(table[(size_t)id * D + i]) * scale;
+        x[(size_t)blockIdx.x * D + i] = v;
+        xa[(size_t)blockIdx.x * D + i] = __float2bfloat16_rn(v);
+    }
+}
+
 __global__ void k_add_one(float* w, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) w[i] += 1.0f;
@@ -320,9 +334,20 @@ int alloc_runtime(zl_kodupel* m) {
     return ZL_OK;
 }
 
-// Programmatic dependent launch only for the skinny Linears of steps with few rows (see the measurements noted in
-// dekipel_runner.cu: early CTAs of the other kernel classes take SM slots from the kernel they wait for).
-int pdl_skinny(const zl_kodupel* m) { return m->cfg.use_pdl ? 1 : 0; }
+// Which kernels of a step of at most 8 rows are launched with a programmatic dependency: 1 skinny Linears, 2 other GEMMs
+// (tanh, grouped), 4 row kernels (norms, combine, head prep, router, plan), 8 attention, 16 recurrence, 32 the tail.
+// Larger steps use none (early CTAs of a dependent kernel take SM slots from the kernel they wait for).
+// ZL_KODUPEL_PDL_MASK overrides the default.
+constexpr int kDefaultPdlMask = 1;
+int pdl_mask() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("ZL_KODUPEL_PDL_MASK");
+        v = e ? atoi(e) : kDefaultPdlMask;
+    }
+    return v;
+}
+int pdl_for(const zl_kodupel* m, int bit, int T) { return (m->cfg.use_pdl && T <= 8 && (pdl_mask() & bit)) ? 1 : 0; }
 
 // y (M, N) = x (M, K) @ w (N, K)^T + bias, optional tanh.  bias_f32 / bias_act are the same numbers in two types.
 int linear(zl_kodupel* m, const void* x, int K, const void* w, int N, const float* bias_f32, const void* bias_act, void* y,
@@ -331,25 +356,23 @@ int linear(zl_kodupel* m, const void* x, int K, const void* w, int N, const floa
     static const bool no_skinny = getenv("ZL_KODUPEL_NO_SKINNY") != nullptr;
     if (!no_skinny && c.dtype != ZL_F32 && epi == ZL_GEMM_EPI_NONE && M <= 32 && K % 32 == 0 && N >= 64 && (!bias_f32 || bias_act) &&
         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0)
-        return zl_dense_gemm_skinny_act(x, K, w, bias_act, y, M, N, K, c.dtype, out_dtype, 0, M <= 8 ? pdl_skinny(m) : 0, m->stream);
-    return zl_gemm_nt_bias(x, K, w, K, bias_f32, y, N, M, N, K, c.dtype, out_dtype, epi, 0, m->stream);
+        return zl_dense_gemm_skinny_act(x, K, w, bias_act, y, M, N, K, c.dtype, out_dtype, 0, pdl_for(m, 1, M), m->stream);
+    return zl_gemm_nt_bias(x, K, w, K, bias_f32, y, N, M, N, K, c.dtype, out_dtype, epi, pdl_for(m, 2, M), m->stream);
 }
 
 int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_run, int max_len) {
     const auto& c = m->cfg;
     const int D = c.width, dt = c.dtype;
     cudaStream_t st = m->stream;
+    const int pg = pdl_for(m, 2, T), pr = pdl_for(m, 4, T), pa = pdl_for(m, 8, T), pd = pdl_for(m, 16, T), pt = pdl_for(m, 32, T);
     const void* xin = dt == ZL_F32 ? (const void*)m->x : (const void*)m->xa;   // what the Linears read
     void* xa_out = dt == ZL_F32 ? nullptr : m->xa;
     if (dt == ZL_F32) {
         ZL_CHECK_CUDA(launch(k_embed_f32<float>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
                              (const float*)m->embed, m->x, D, c.vocab, c.embed_scale));
     } else {
-        ZL_CHECK_CUDA(launch(k_embed_f32<__nv_bfloat16>, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
-                             (const __nv_bfloat16*)m->embed, m->x, D, c.vocab, c.embed_scale));
-        const size_t n = (size_t)T * D;
-        ZL_CHECK_CUDA(launch(k_convert<float, __nv_bfloat16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, false,
-                             (const float*)m->x, (__nv_bfloat16*)m->xa, n));
+        ZL_CHECK_CUDA(launch(k_embed_scaled_pair, dim3(T), dim3(128), 0, st, false, (const int32_t*)m->d_tokens,
+                             (const __nv_bfloat16*)m->embed, m->x, (__nv_bfloat16*)m->xa, D, c.vocab, c.embed_scale));
     }
     for (int l = 0; l < c.num_layers; ++l) {
         KLayer& L = m->layers[l];
@@ -359,11 +382,11 @@ int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_run, int 
         if (lc.type == ZL_MIXER_ATTENTION) {
             RCHECK(zl_qkv_headnorm_rope_append(m->proj, L.n_in, L.q_off, L.k_off, L.v_off, H, lc.kv_heads, lc.dim, lc.vdim,
                                                L.q_norm, L.k_norm, L.inv_freq, lc.rot_dims, L.mscale, c.eps, m->q, L.k_addrs,
-                                               L.v_addrs, m->d_slots, m->d_pos, T, dt, 0, st));
+                                               L.v_addrs, m->d_slots, m->d_pos, T, dt, pr, st));
             const int splits = zl_sink_attention_splits(T, H, lc.kv_heads, max_len);
             RCHECK(zl_sink_attention(m->q, L.k_addrs, L.v_addrs, m->d_slots, m->d_pos, nullptr, m->proj + L.g_off, L.n_in,
                                      lc.scale, m->att, T, H, lc.kv_heads, lc.dim, lc.vdim, splits, m->attn_ws, m->attn_ws_bytes,
-                                     m->d_run0, m->d_runlen, n_runs, max_run, dt, 0, st));
+                                     m->d_run0, m->d_runlen, n_runs, max_run, dt, pa, st));
             RCHECK(linear(m, m->att, H * lc.vdim, L.o, D, L.o_b, L.o_b_act, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
         } else {
             const int hd = H * lc.dim;
@@ -371,21 +394,21 @@ int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_run, int 
             RCHECK(linear(m, m->z1, lc.decay_rank, L.w2, hd, L.w0, L.w0_act, m->dlog, T, ZL_F32, ZL_GEMM_EPI_NONE));
             RCHECK(zl_delta_rule(m->proj + L.q_off, L.n_in, m->proj + L.k_off, L.n_in, m->proj + L.v_off, L.n_in,
                                  m->proj + L.a_off, L.n_in, m->dlog, hd, expf(-0.5f), 1e-6f, m->d_run0, m->d_runlen, n_runs,
-                                 m->d_slots, m->d_pos, L.state.addrs, m->orec, hd, H, lc.dim, lc.dim, T, m->delta_ws, m->delta_ws_bytes, 0, st));
+                                 m->d_slots, m->d_pos, L.state.addrs, m->orec, hd, H, lc.dim, lc.dim, T, m->delta_ws, m->delta_ws_bytes, pd, st));
             RCHECK(zl_head_rmsnorm_gate(m->orec, hd, L.out_norm, m->proj + L.g_off, L.n_in, m->att, hd, T, H, lc.dim, c.eps, dt,
-                                        0, st));
+                                        pr, st));
             RCHECK(linear(m, m->att, hd, L.o, D, nullptr, nullptr, m->y, T, ZL_F32, ZL_GEMM_EPI_NONE));
         }
-        RCHECK(zl_rmsnorm_residual_combine(m->y, D, nullptr, 1, L.norm1, m->x, D, xa_out, dt, T, D, c.eps, 0, st));
+        RCHECK(zl_rmsnorm_residual_combine(m->y, D, nullptr, 1, L.norm1, m->x, D, xa_out, dt, T, D, c.eps, pr, st));
         if (lc.experts > 0) {
             const int E = lc.experts, top = lc.top, F = lc.ff;
             RCHECK(zl_moe_route(m->x, D, L.router, L.correction, m->top_e, m->top_w, m->grp_off, m->list_token, m->list_pair,
-                                T, D, E, top, ZL_MOE_SCORE_SIGMOID, 0, 0, st));
+                                T, D, E, top, ZL_MOE_SCORE_SIGMOID, 0, pr, st));
             RCHECK(zl_gemm_nt_grouped(xin, D, m->list_token, L.w_gu, D, (long long)2 * F * D, m->act, F, nullptr, m->grp_off, E,
-                                      T, 2 * F, D, dt, dt, ZL_GEMM_EPI_GLU_CLAMP, lc.limit, 1.702f, 1.0f, 0, st));
+                                      T, 2 * F, D, dt, dt, ZL_GEMM_EPI_GLU_CLAMP, lc.limit, 1.702f, 1.0f, pg, st));
             RCHECK(zl_gemm_nt_grouped(m->act, F, nullptr, L.w_down, F, (long long)D * F, m->ypair, D, m->list_pair, m->grp_off,
-                                      E, T, D, F, dt, ZL_F32, ZL_GEMM_EPI_NONE, 0.f, 1.f, 0.f, 0, st));
-            RCHECK(zl_rmsnorm_residual_combine(m->ypair, D, m->top_w, top, L.norm2, m->x, D, xa_out, dt, T, D, c.eps, 0, st));
+                                      E, T, D, F, dt, ZL_F32, ZL_GEMM_EPI_NONE, 0.f, 1.f, 0.f, pg, st));
+            RCHECK(zl_rmsnorm_residual_combine(m->ypair, D, m->top_w, top, L.norm2, m->x, D, xa_out, dt, T, D, c.eps, pr, st));
         }
         if (m->capture && m->layer_dump)
             ZL_CHECK_CUDA(cudaMemcpyAsync(m->layer_dump + (size_t)l * m->tcap * D, m->x, (size_t)T * D * 4,
@@ -394,9 +417,9 @@ int enqueue_step(zl_kodupel* m, int T, int n_want, int n_runs, int max_run, int 
     if (n_want > 0) {
         ZL_CHECK_CUDA(launch(k_gather_rows_f32, dim3(n_want), dim3(128), 0, st, false, (const float*)m->x,
                              (const int32_t*)m->d_want, m->xw, D));
-        RCHECK(zl_group_rmsnorm(m->xw, D, m->final_norm, m->xn, D, n_want, D, 1, c.eps, dt, 0, st));
+        RCHECK(zl_group_rmsnorm(m->xw, D, m->final_norm, m->xn, D, n_want, D, 1, c.eps, dt, pt, st));
         RCHECK(linear(m, m->xn, D, m->head, c.vocab, nullptr, nullptr, m->logits, n_want, ZL_F32, ZL_GEMM_EPI_NONE));
-        RCHECK(zl_argmax(m->logits, m->d_next, n_want, c.vocab, m->argmax_ws, zl_argmax_workspace_bytes(n_want), 0, st));
+        RCHECK(zl_argmax(m->logits, m->d_next, n_want, c.vocab, m->argmax_ws, zl_argmax_workspace_bytes(n_want), pt, st));
     }
     return ZL_OK;
 }
