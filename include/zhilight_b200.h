@@ -516,8 +516,8 @@ int zl_dekipel_stats(zl_dekipel_t* m, double* weight_bytes, int* kernels_per_ste
 /* Rotation frequencies f_i = base^(-2i/dims), i < dims/2, with YaRN scaling when factor > 0: with
  * dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims-1) and
  * ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i), and
- * cos / sin are scaled by mscale = 0.1 ln(factor) + 1 (1 without scaling).  Host function; out (dims/2) floats. */
-int zl_rope_inv_freq_yarn(double base, int dims, double factor, double original, double fast, double slow, float* out,
+ * cos / sin are scaled by mscale = 0.1 ln(factor) + 1 (1 without scaling).  Host function; out (dims/2) doubles. */
+int zl_rope_inv_freq_yarn(double base, int dims, double factor, double original, double fast, double slow, double* out,
                           float* mscale);
 /* From a fused projection row proj[t] (fp32) to attention operands: per query head RMS norm over `dim` times q_weight
  * (dim), rotation of the first rot_dims dimensions in adjacent pairs (2i, 2i+1) by pos[t] * inv_freq[i] (cos, sin times
@@ -525,7 +525,7 @@ int zl_rope_inv_freq_yarn(double base, int dims, double factor, double original,
  * k_addrs[slot[t]] ((max_seq, kv_heads, dim)), and every value head divided by its RMS over `vdim` -> row pos[t] of
  * v_addrs[slot[t]] ((max_seq, kv_heads, vdim)). */
 int zl_qkv_headnorm_rope_append(const float* proj, long long ldp, int q_off, int k_off, int v_off, int heads, int kv_heads,
-                                int dim, int vdim, const float* q_weight, const float* k_weight, const float* inv_freq,
+                                int dim, int vdim, const float* q_weight, const float* k_weight, const double* inv_freq,
                                 int rot_dims, float mscale, float eps, void* q_out, void* const* k_addrs,
                                 void* const* v_addrs, const int32_t* slot, const int32_t* pos, int T, int dtype, int pdl,
                                 zl_stream_t stream);

@@ -144,7 +144,7 @@ def test_rotation_frequencies(lib):
         cos, sin = orc.rotation_tables(2, dims, base, scd)
         mag = math.hypot(cos[1, 0], sin[1, 0])
         assert abs(ms - mag) < 1e-6
-        assert np.allclose(np.arctan2(sin[1], cos[1]), np.float64(f), rtol=2e-7, atol=0)
+        assert np.allclose(np.arctan2(sin[1], cos[1]), f, rtol=1e-12, atol=0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -36,7 +36,8 @@ struct KLayer {
     float* o_b = nullptr;
     void* o_b_act = nullptr;
     // attention
-    float *q_norm = nullptr, *k_norm = nullptr, *inv_freq = nullptr;
+    float *q_norm = nullptr, *k_norm = nullptr;
+    double* inv_freq = nullptr;
     float mscale = 1.f;
     SlotCache kcache, vcache;
     void **k_addrs = nullptr, **v_addrs = nullptr;   // own or the source layer's
@@ -221,11 +222,11 @@ int finalize_layer(zl_kodupel* m, int l) {
         RCHECK(take_f32(m, mx + "o.b", 1, D, &L.o_b));
         RCHECK(bias_act_copy(m, L.o_b, D, &L.o_b_act));
         if (lc.rot_dims > 0) {
-            std::vector<float> f(lc.rot_dims / 2);
+            std::vector<double> f(lc.rot_dims / 2);
             RCHECK(zl_rope_inv_freq_yarn(lc.rot_base, lc.rot_dims, lc.yarn_factor, lc.yarn_original, lc.yarn_fast, lc.yarn_slow,
                                          f.data(), &L.mscale));
-            RCHECK(dmalloc((void**)&L.inv_freq, f.size() * 4));
-            ZL_CHECK_CUDA(cudaMemcpy(L.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice));
+            RCHECK(dmalloc((void**)&L.inv_freq, f.size() * 8));
+            ZL_CHECK_CUDA(cudaMemcpy(L.inv_freq, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
         }
     } else {
         const int d = lc.dim, hd = H * d, R = lc.decay_rank;

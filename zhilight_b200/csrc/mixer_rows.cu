@@ -1,4 +1,5 @@
-// Token-wise pieces of mixers that work per head, all in fp32 with stores rounded to the activation dtype:
+// Token-wise pieces of mixers that work per head, all in fp32 (rotation angles in double) with stores rounded to the
+// activation dtype:
 //   * the step from a fused q | k | v projection row to attention operands: RMS norm per head over the head size with a
 //     weight shared by the heads (queries, keys), a weightless RMS norm of every value head, a rotation of the first
 //     `rot_dims` dimensions of queries and keys in adjacent pairs (2i, 2i+1) by pos * inv_freq[i] with cos / sin scaled
@@ -17,7 +18,8 @@ struct QkvPrepP {
     long long ldp;
     int q_off, k_off, v_off;   // k_off < 0: the layer has no keys / values of its own
     int H, G, d, vd, rot_dims;
-    const float *q_w, *k_w, *inv_freq;
+    const float *q_w, *k_w;
+    const double* inv_freq;
     float mscale, eps;
     void* q_out;               // (T, H * d)
     void* const* k_addrs;      // slot -> (max_seq, G, d)
@@ -69,8 +71,11 @@ __global__ void __launch_bounds__(128) k_qkv_headnorm_rope_append(QkvPrepP p) {
     // rotated pairs: lane handles pair i = (2i, 2i + 1)
     for (int i = lane; 2 * i < rot; i += 32) {
         const float u = src[2 * i] * r * w[2 * i], v = src[2 * i + 1] * r * w[2 * i + 1];
-        const float ang = (float)pos * p.inv_freq[i];
-        const float cs = cosf(ang) * p.mscale, sn = sinf(ang) * p.mscale;
+        // the angle and its cos / sin in double: at position 1000 a float angle is already off by 3e-5 rad, which a sharp
+        // score multiplies; rot_dims / 2 evaluations per head cost nothing beside the projections
+        double sd, cd;
+        sincos((double)pos * p.inv_freq[i], &sd, &cd);
+        const float cs = (float)(cd * (double)p.mscale), sn = (float)(sd * (double)p.mscale);
         dst[2 * i] = from_f32<TO>(u * cs - v * sn);
         dst[2 * i + 1] = from_f32<TO>(v * cs + u * sn);
     }
@@ -174,7 +179,7 @@ using namespace zl;
 
 extern "C" int zl_qkv_headnorm_rope_append(const float* proj, long long ldp, int q_off, int k_off, int v_off, int heads,
                                            int kv_heads, int dim, int vdim, const float* q_weight, const float* k_weight,
-                                           const float* inv_freq, int rot_dims, float mscale, float eps, void* q_out,
+                                           const double* inv_freq, int rot_dims, float mscale, float eps, void* q_out,
                                            void* const* k_addrs, void* const* v_addrs, const int32_t* slot,
                                            const int32_t* pos, int T, int dtype, int pdl, zl_stream_t stream) {
     ZL_CHECK_ARG(proj && q_weight && q_out && slot && pos && T > 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0);
@@ -232,7 +237,7 @@ extern "C" int zl_rmsnorm_residual_combine(const float* parts, long long ldp, co
 }
 
 extern "C" int zl_rope_inv_freq_yarn(double base, int dims, double factor, double original, double fast, double slow,
-                                     float* out, float* mscale) {
+                                     double* out, float* mscale) {
     ZL_CHECK_ARG(base > 1.0 && dims >= 0 && dims % 2 == 0 && (dims == 0 || out));
     const int half = dims / 2;
     const double kPi = 3.14159265358979323846;
@@ -249,7 +254,7 @@ extern "C" int zl_rope_inv_freq_yarn(double base, int dims, double factor, doubl
             const double ramp = fmin(fmax((i - lo) / fmax(hi - lo, 0.001), 0.0), 1.0);
             f = f / factor * ramp + f * (1 - ramp);
         }
-        out[i] = (float)f;
+        out[i] = f;
     }
     if (mscale) *mscale = factor > 0 ? (float)(0.1 * log(factor) + 1.0) : 1.0f;
     return ZL_OK;

@@ -505,23 +505,23 @@ def gemm_nt_grouped(x, w, group_offsets, rows_out, x_rows=None, y_rows=None, out
 
 
 def rope_inv_freq_yarn(base, dims, factor=0.0, original=0.0, fast=0.0, slow=0.0):
-    """-> (frequencies (dims / 2) float32 numpy array, cos / sin scale)."""
+    """-> (frequencies (dims / 2) float64 numpy array, cos / sin scale)."""
     import numpy as np
-    out = np.zeros(max(dims // 2, 1), dtype=np.float32)
+    out = np.zeros(max(dims // 2, 1), dtype=np.float64)
     ms = ctypes.c_float()
     _lib.call("zl_rope_inv_freq_yarn", float(base), dims, float(factor), float(original), float(fast), float(slow),
-              out.ctypes.data_as(ctypes.c_void_p), ctypes.cast(ctypes.byref(ms), ctypes.c_void_p))
+              out.ctypes.data_as(ctypes.POINTER(ctypes.c_double)), ctypes.cast(ctypes.byref(ms), ctypes.c_void_p))
     return out[:dims // 2], ms.value
 
 
 def qkv_headnorm_rope_append(proj, q_off, k_off, v_off, heads, kv_heads, dim, vdim, q_weight, k_weight, inv_freq, rot_dims,
                              mscale, eps, k_cache, v_cache, k_table, v_table, slot, pos, dtype):
-    """proj (T, ld) fp32 -> q (T, heads * dim) of `dtype`; keys / values go to rows (slot, pos) of the caches
+    """proj (T, ld) fp32, inv_freq (rot_dims / 2) float64 -> q (T, heads * dim) of `dtype`; keys / values go to rows (slot, pos) of the caches
     (slots, rows, kv_heads * dim) / (slots, rows, kv_heads * vdim) unless k_off < 0."""
     t, ldp = proj.shape
     q = torch.empty((t, heads * dim), dtype=dtype, device=proj.device)
     _lib.call("zl_qkv_headnorm_rope_append", _p(proj), ldp, q_off, k_off, v_off, heads, kv_heads, dim, vdim, _p(q_weight),
-              _p(k_weight), _p(inv_freq), rot_dims, mscale, eps, _p(q), _p(k_table), _p(v_table), _p(slot), _p(pos), t, _dt(q),
+              _p(k_weight), ctypes.cast(_p(inv_freq), ctypes.POINTER(ctypes.c_double)), rot_dims, mscale, eps, _p(q), _p(k_table), _p(v_table), _p(slot), _p(pos), t, _dt(q),
               0, _stream())
     return q
 
