@@ -28,6 +28,7 @@ struct GemmP {
     const int32_t* grp_off = nullptr; // grouped mode: rows grp_off[b] .. grp_off[b+1] of the sorted list belong to problem b
     const int32_t* x_rows = nullptr;  // sorted index -> row of x (identity when null)
     const int32_t* y_rows = nullptr;  // sorted index -> row of y (identity when null)
+    int act_tanh = 0;                 // few-rows kernel without the gated unit: tanh of the (biased) sum
     float limit = 0.f, alpha = 1.f, beta = 0.f;   // gated unit: g = min(gate, limit), u = clamp(up, +-limit), g sigmoid(alpha g) (u + beta)
 };
 
@@ -343,7 +344,12 @@ __global__ void __launch_bounds__(256) k_gemm_grouped_small(GemmP p) {
 #pragma unroll
             for (int m = 0; m < 8; ++m) {
                 float v = warp_sum(acc[m]);
-                if (GLU) v = glu_clamp(v, warp_sum(acc2[m]), p);
+                if (GLU) {
+                    v = glu_clamp(v, warp_sum(acc2[m]), p);
+                } else {
+                    if (p.bias) v += p.bias[(size_t)b * p.bb + n];
+                    if (p.act_tanh) v = tanhf(v);
+                }
                 if (lane == m) mine = v;
             }
             if (lane < mc) {
@@ -528,6 +534,15 @@ static int gemm_dispatch(GemmP p, int batch, int in_dtype, int out_dtype, int ep
         else
             e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, batch, pairs, pdl != 0, stream)
                                     : launch_grouped_small<__half, __half>(p, batch, pairs, pdl != 0, stream);
+    } else if (!grouped && epilogue == ZL_GEMM_EPI_TANH && batch == 1 && M <= 8 && vx && vw && K % 8 == 0 &&
+               (size_t)8 * K * 2 <= 160 * 1024) {   // a narrow tanh projection of a decode step: one column per warp, loads in flight
+        p.act_tanh = 1;
+        if (in_dtype == ZL_BF16)
+            e = out_dtype == ZL_F32 ? launch_grouped_small<__nv_bfloat16, float>(p, 1, false, pdl != 0, stream)
+                                    : launch_grouped_small<__nv_bfloat16, __nv_bfloat16>(p, 1, false, pdl != 0, stream);
+        else
+            e = out_dtype == ZL_F32 ? launch_grouped_small<__half, float>(p, 1, false, pdl != 0, stream)
+                                    : launch_grouped_small<__half, __half>(p, 1, false, pdl != 0, stream);
     } else if (!grouped && !pairs && M <= 8 && vx && vw && (size_t)M * K * 2 <= 48 * 1024) {   // few rows: stream the weights once per column
         if (in_dtype == ZL_BF16)
             e = out_dtype == ZL_F32 ? launch_small_m<__nv_bfloat16, float>(p, batch, epilogue, pdl != 0, stream)

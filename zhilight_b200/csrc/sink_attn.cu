@@ -458,14 +458,17 @@ __global__ void __launch_bounds__(128) k_sink_attn_merge(SinkAttnP p) {
     float gate = 1.0f;
     if (p.gate) gate = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.ldg + h]));
     T* out = static_cast<T*>(p.out) + ((size_t)t * p.H + h) * p.vd;
-    for (int c0 = 0; c0 < p.vd; c0 += 32) {   // every lane runs the shuffles; only lanes with a column load and store
-        const int c = c0 + lane;
+    float wv[32];   // every split's weight in every lane: the loads below do not wait for shuffles
+#pragma unroll
+    for (int s = 0; s < 32; ++s) wv[s] = __shfl_sync(0xffffffffu, wgt, s);
+    for (int c = lane; c < p.vd; c += 32) {
+        float v[32];
+#pragma unroll
+        for (int s = 0; s < 32; ++s) v[s] = s < p.splits ? part[(size_t)s * stride + 2 + c] : 0.f;   // all loads in flight
         float o = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float w = __shfl_sync(0xffffffffu, wgt, s);
-            if (c < p.vd) o = fmaf(part[(size_t)s * stride + 2 + c], w, o);
-        }
-        if (c < p.vd) out[c] = from_f32<T>(o / L * gate);
+#pragma unroll
+        for (int s = 0; s < 32; ++s) o = fmaf(v[s], wv[s], o);   // splits in order; absent ones add 0 * 0
+        out[c] = from_f32<T>(o / L * gate);
     }
 }
 
